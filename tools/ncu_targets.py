@@ -1,6 +1,6 @@
 """Short single-GPU workload that launches each kernel family once per iteration, for ``ncu`` (one capture per call):
 
-    python tools/ncu_targets.py && ncu --set full --clock-control none --import-source on \
+    python tools/ncu_targets.py && ncu --set full --clock-control none \
         -k regex:'gemm_pair_x_kernel|gemm_pair_kernel|rs_adam_emu|push_emu|pull_emu|attn_fwd_kernel|attn_bwd|all_gather_emu|fp_gemv' \
         -s 36 -c 18 -o gpurun_out/prof_r2 python tools/ncu_targets.py
 
