@@ -1,0 +1,586 @@
+// seq_mixers.cu — ragged-batch kernels for layer stacks that mix attention with recurrent sequence mixers
+// (gated delta rule, state-space duality) and keep the residual stream in fp32.
+//
+// Every kernel works on a ragged batch: `tok_seq[t]` / `tok_pos[t]` give each token's sequence slot in the batch and
+// its position in its sequence, `seq_info[s] = {first row, rows, tokens already seen, state slot}` describes each
+// sequence, `block_tables[s]` its pages of the key/value cache.  `T` is the activation type (bf16 when serving,
+// float for exact evaluation); everything that the recurrences, norms and softmax touch is fp32 in both.
+//
+//   embed_sinusoid        token row * scale + sinusoidal position vector            -> fp32 residual
+//   resid_norm_step       residual += rms(y) * w_post (+ extra);  out = rms(residual) * w_pre   (one pass per row)
+//   qk_norm_append        bias + per-head unit-RMS of q and k, q -> fp32, k / v -> paged cache
+//   sink_attention        causal or chunk-local softmax attention over the paged cache with a per-head sink logit
+//   conv_silu / conv_state_update   short causal per-channel filter with its carried inputs per state slot
+//   unit_norm_heads, recurrence_gates   per-head L2 normalisation; decay / write strength of the recurrences
+//   linear_recurrence     S <- a S;  u = b (v - [delta] S^T k);  S <- S + k u^T;  o = S^T q (+ D v), state per slot
+//   group_norm_gate       RMS norm over channel groups combined with a SiLU gate (before or after the norm)
+//   gated_act_rows        act(gate) * up for any width and fp32 or bf16 rows
+#include "sxb_common.cuh"
+
+namespace sxb {
+namespace seqmix {
+
+
+
+#define SEQMIX_DISPATCH(dtype, ...)                \
+  do {                                             \
+    if ((dtype) == 0) {                         \
+      using T = float;                             \
+      __VA_ARGS__;                                 \
+    } else if ((dtype) == 2) {                 \
+      using T = __nv_bfloat16;                     \
+      __VA_ARGS__;                                 \
+    } else {                                       \
+      return SXB_ERR_UNSUPPORTED;                  \
+    }                                              \
+  } while (0)
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 30.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void __launch_bounds__(256)
+embed_sinusoid_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const T* __restrict__ table,
+                      float* __restrict__ out, int width, float scale, float base) {
+  const int t = blockIdx.x;
+  const T* row = table + (long long)ids[t] * width;
+  const float p = (float)pos[t];
+  const float lb = log2f(base);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const int i = c >> 1;
+    const float freq = exp2f(-(2.f * (float)i / (float)width) * lb);
+    const float ang = p * freq;
+    const float pe = (c & 1) ? cosf(ang) : sinf(ang);
+    out[(long long)t * width + c] = to_f32<T>(row[c]) * scale + pe;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ residual + norms
+// One CTA per row.  y (optional): residual += y / rms(y) * w_post.  extra (optional): residual += extra.
+// w_pre (optional): out = residual / rms(residual) * w_pre.
+template <typename T>
+__global__ void __launch_bounds__(256)
+resid_norm_step_kernel(float* __restrict__ resid, const T* __restrict__ y, const T* __restrict__ w_post,
+                       const float* __restrict__ extra, const T* __restrict__ w_pre, T* __restrict__ out, int width,
+                       float eps) {
+  __shared__ float red[32];
+  const long long base = (long long)blockIdx.x * width;
+  float* r = resid + base;
+  float inv_y = 0.f;
+  if (y != nullptr) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float v = to_f32<T>(y[base + c]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    inv_y = 1.f / sqrtf(ss / (float)width + eps);
+  }
+  float ss2 = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = r[c];
+    if (y != nullptr) v += to_f32<T>(y[base + c]) * inv_y * to_f32<T>(w_post[c]);
+    if (extra != nullptr) v += extra[base + c];
+    if (y != nullptr || extra != nullptr) r[c] = v;
+    ss2 += v * v;
+  }
+  if (w_pre == nullptr) return;
+  ss2 = block_sum(ss2, red);
+  const float inv = 1.f / sqrtf(ss2 / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[base + c] = from_f32<T>(r[c] * inv * to_f32<T>(w_pre[c]));
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+// One CTA per token, one warp per head slot (Hq query heads, G key heads, G value heads in the fused projection row).
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ bias, float* __restrict__ q_out,
+                      T* __restrict__ kcache, T* __restrict__ vcache, const int* __restrict__ tok_seq,
+                      const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
+                      int Hq, int G, int d, int dv, float eps, int normalize) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T* row = qkv + (long long)t * ld;
+  const int pos = tok_pos[t];
+  const long long page = tables[(long long)tok_seq[t] * max_blocks + pos / block_size];
+  const long long slot = page * block_size + pos % block_size;
+  for (int s = warp; s < Hq + 2 * G; s += nw) {
+    if (s < Hq + G) {
+      const int col = s * d;     // q heads then k heads are contiguous with the same head size
+      float ss = 0.f;
+      for (int c = lane; c < d; c += 32) {
+        const float v = to_f32<T>(row[col + c]) + (bias ? to_f32<T>(bias[col + c]) : 0.f);
+        ss += v * v;
+      }
+      ss = warp_sum(ss);
+      const float inv = normalize ? 1.f / sqrtf(ss / (float)d + eps) : 1.f;
+      for (int c = lane; c < d; c += 32) {
+        const float v = (to_f32<T>(row[col + c]) + (bias ? to_f32<T>(bias[col + c]) : 0.f)) * inv;
+        if (s < Hq) q_out[((long long)t * Hq + s) * d + c] = v;
+        else kcache[(slot * G + (s - Hq)) * d + c] = from_f32<T>(v);
+      }
+    } else {
+      const int g = s - Hq - G, col = (Hq + G) * d + g * dv;
+      for (int c = lane; c < dv; c += 32) {
+        const float v = to_f32<T>(row[col + c]) + (bias ? to_f32<T>(bias[col + c]) : 0.f);
+        vcache[(slot * G + g) * dv + c] = from_f32<T>(v);
+      }
+    }
+  }
+}
+
+constexpr int kMaxVPerLane = 8;      // value head size <= 256
+
+// One warp per (token, query head).  Keys lo..pos of the token's sequence, lo = start of the token's chunk
+// (chunk > 0) or 0.  The softmax denominator starts from exp(sink[h]): a logit without a key or a value.
+template <typename T>
+__global__ void __launch_bounds__(128)
+sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
+                      const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
+                      const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
+                      int Hq, int G, int d, int dv, float scale, int chunk) {
+  extern __shared__ float qs[];      // [warps][d]
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int h = blockIdx.y * nw + warp;
+  if (h >= Hq) return;
+  float* myq = qs + warp * d;
+  for (int c = lane; c < d; c += 32) myq[c] = q[((long long)t * Hq + h) * d + c];
+  __syncwarp();
+  const int g = h / (Hq / G);
+  const int pos = tok_pos[t];
+  const int* tab = tables + (long long)tok_seq[t] * max_blocks;
+  const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
+  float acc[kMaxVPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxVPerLane; ++i) acc[i] = 0.f;
+  for (int j0 = lo; j0 <= pos; j0 += 32) {
+    const int j = j0 + lane;
+    float s = -INFINITY;
+    if (j <= pos) {
+      const long long slot = (long long)tab[j / block_size] * block_size + j % block_size;
+      const T* kr = kcache + (slot * G + g) * d;
+      float a = 0.f;
+      for (int c = 0; c < d; ++c) a += myq[c] * to_f32<T>(kr[c]);
+      s = a * scale;
+    }
+    const float mt = warp_max(s);
+    const float mn = fmaxf(m, mt);
+    const float corr = expf(m - mn);     // m is finite or (no sink, first tile) -inf with l = 0 and acc = 0
+    const float p = (j <= pos) ? expf(s - mn) : 0.f;
+    l = l * (m == -INFINITY ? 0.f : corr) + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < kMaxVPerLane; ++i) acc[i] *= (m == -INFINITY ? 0.f : corr);
+    m = mn;
+    const int n = min(32, pos - j0 + 1);
+    for (int jj = 0; jj < n; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const int jk = j0 + jj;
+      const long long slot = (long long)tab[jk / block_size] * block_size + jk % block_size;
+      const T* vr = vcache + (slot * G + g) * dv;
+#pragma unroll
+      for (int i = 0; i < kMaxVPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) acc[i] += pj * to_f32<T>(vr[c]);
+      }
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVPerLane; ++i) {
+    const int c = lane + 32 * i;
+    if (c < dv) out[((long long)t * Hq + h) * dv + c] = from_f32<T>(acc[i] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ short convolution
+constexpr int kMaxTaps = 16;
+
+// out[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * x[t-j, c]); x before this batch's rows comes from the slot's carried
+// inputs (state [slots, taps-1, C], last row = most recent), x before the sequence's start is zero.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_silu_kernel(const T* __restrict__ x, long long ld, const T* __restrict__ w, const T* __restrict__ bias,
+                 const T* __restrict__ state, const int* __restrict__ seq_info, const int* __restrict__ tok_seq,
+                 float* __restrict__ out, int C, int taps) {
+  const int t = blockIdx.x;
+  const int* si = seq_info + 4 * tok_seq[t];
+  const int local = t - si[0], seen = si[2];
+  const T* st = state + (long long)si[3] * (taps - 1) * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    float a = bias ? to_f32<T>(bias[c]) : 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int src = local - j;
+      float v = 0.f;
+      if (src >= 0) v = to_f32<T>(x[(long long)(t - j) * ld + c]);
+      else if (seen + src >= 0) v = to_f32<T>(st[(long long)(taps - 1 + src) * C + c]);
+      a += to_f32<T>(w[(long long)c * taps + (taps - 1 - j)]) * v;
+    }
+    out[(long long)t * C + c] = silu_f(a);
+  }
+}
+
+// After conv_silu of a batch: each slot keeps the last taps-1 inputs of (carried inputs ++ this batch's rows).
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_state_update_kernel(const T* __restrict__ x, long long ld, T* __restrict__ state,
+                         const int* __restrict__ seq_info, int C, int taps) {
+  const int* si = seq_info + 4 * blockIdx.x;
+  const int first = si[0], n = si[1], seen = si[2];
+  T* st = state + (long long)si[3] * (taps - 1) * C;
+  const int keep = taps - 1;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    T vals[kMaxTaps];
+    for (int j = 0; j < keep; ++j) {
+      const int i = n + j;           // index into carried (keep rows) ++ new (n rows)
+      if (i >= keep) vals[j] = x[(long long)(first + i - keep) * ld + c];
+      else vals[j] = (seen + (i - keep) >= 0) ? st[(long long)i * C + c] : from_f32<T>(0.f);
+    }
+    for (int j = 0; j < keep; ++j) st[(long long)j * C + c] = vals[j];
+  }
+}
+
+// x[t, col0 + h*dim .. +dim] <- x * mult / sqrt(sum(x^2) + eps); one warp per (token, head).
+__global__ void __launch_bounds__(128)
+unit_norm_heads_kernel(float* __restrict__ x, long long ld, int col0, int n_heads, int dim, float mult, float eps,
+                       int n_tokens) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= n_tokens * n_heads) return;
+  float* p = x + (long long)(idx / n_heads) * ld + col0 + (idx % n_heads) * dim;
+  float ss = 0.f;
+  for (int c = lane; c < dim; c += 32) ss += p[c] * p[c];
+  ss = warp_sum(ss);
+  const float inv = mult / sqrtf(ss + eps);
+  for (int c = lane; c < dim; c += 32) p[c] *= inv;
+}
+
+// mode 0 (delta rule):  beta = sigmoid(b_raw), decay = exp(-exp(A_log) * softplus(a_raw + dt_bias))
+// mode 1 (state space): dt = softplus(a_raw + dt_bias), beta = dt, decay = exp(-exp(A_log) * dt)
+template <typename T>
+__global__ void __launch_bounds__(256)
+recurrence_gates_kernel(const T* __restrict__ a_raw, const T* __restrict__ b_raw, long long ld,
+                        const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ decay,
+                        float* __restrict__ beta, int H, int n_tokens, int mode) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * H) return;
+  const int t = i / H, h = i % H;
+  const float dt = softplus_f(to_f32<T>(a_raw[(long long)t * ld + h]) + dt_bias[h]);
+  decay[i] = expf(-expf(A_log[h]) * dt);
+  beta[i] = mode == 0 ? sigmoid_f(to_f32<T>(b_raw[(long long)t * ld + h])) : dt;
+}
+
+// ------------------------------------------------------------------------------------------------ recurrence
+// State per (slot, head): dv columns of n floats, stored [dv][n].  Each output column evolves on its own:
+//   s <- a s;  u = b (v_c - [delta] s.k);  s <- s + k u;  o_c = s.q (+ D v_c)
+// A column is held by LPC = 8 lanes (n split i = lane + 8 r), 16 columns per CTA; the CTA walks its sequence's rows in
+// order, staging k and q of TB tokens at a time in shared memory.
+constexpr int kLPC = 8, kCols = 16, kTB = 8;
+
+template <int R>
+__global__ void __launch_bounds__(kLPC* kCols)
+linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict__ qvec, long long ldkq,
+                         const float* __restrict__ val, long long ldv, const float* __restrict__ decay,
+                         const float* __restrict__ beta, const float* __restrict__ skip, float* __restrict__ state,
+                         float* __restrict__ out, const int* __restrict__ seq_info, int H, int G, int n, int dv,
+                         int delta) {
+  extern __shared__ float sm[];          // k [TB][n] | q [TB][n] | v [TB][kCols] | decay [TB] | beta [TB]
+  float* sk = sm;
+  float* sq = sk + kTB * n;
+  float* sv = sq + kTB * n;
+  float* sa = sv + kTB * kCols;
+  float* sb = sa + kTB;
+  const int* si = seq_info + 4 * blockIdx.z;
+  const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
+  const int h = blockIdx.y, g = h / (H / G);
+  const int lc = threadIdx.x / kLPC, l = threadIdx.x % kLPC;
+  const int col = blockIdx.x * kCols + lc;
+  const bool live = col < dv;
+  float* sp = state + (((long long)slot * H + h) * dv + (live ? col : 0)) * n;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = l + kLPC * r;
+    S[r] = (live && seen > 0 && i < n) ? sp[i] : 0.f;
+  }
+  const float D = skip ? skip[h] : 0.f;
+  for (int t0 = 0; t0 < rows; t0 += kTB) {
+    const int nt = min(kTB, rows - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
+      const long long row = first + t0 + i / n;
+      sk[i] = kvec[row * ldkq + g * n + i % n];
+      sq[i] = qvec[row * ldkq + g * n + i % n];
+    }
+    for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
+      const int c = blockIdx.x * kCols + i % kCols;
+      sv[i] = c < dv ? val[(long long)(first + t0 + i / kCols) * ldv + h * dv + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < nt; i += blockDim.x) {
+      sa[i] = decay[(long long)(first + t0 + i) * H + h];
+      sb[i] = beta[(long long)(first + t0 + i) * H + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float a = sa[tt], b = sb[tt], v = sv[tt * kCols + lc];
+      const float* kk = sk + tt * n;
+      const float* qq = sq + tt * n;
+      float u = b * v;
+      if (delta) {
+        float dot = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int i = l + kLPC * r;
+          S[r] *= a;
+          if (i < n) dot += S[r] * kk[i];
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        u = b * (v - dot);
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) S[r] *= a;
+      }
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int i = l + kLPC * r;
+        if (i < n) {
+          S[r] += kk[i] * u;
+          o += S[r] * qq[i];
+        }
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      if (live && l == 0) out[(long long)(first + t0 + tt) * H * dv + h * dv + col] = o + D * v;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = l + kLPC * r;
+      if (i < n) sp[i] = S[r];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gated group norm
+// One CTA per (token, group of `gs` channels).  gate_first: z = y * silu(gate); out = z / rms(z) * w.
+// else: out = y / rms(y) * w * silu(gate).  w has `wlen` entries and repeats along the row.
+template <typename T>
+__global__ void __launch_bounds__(128)
+group_norm_gate_kernel(const float* __restrict__ y, const T* __restrict__ gate, long long ldg,
+                       const T* __restrict__ w, int wlen, T* __restrict__ out, int C, int gs, float eps,
+                       int gate_first) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, c0 = blockIdx.y * gs;
+  const float* yr = y + (long long)t * C + c0;
+  const T* gr = gate + (long long)t * ldg + c0;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    float v = yr[c];
+    if (gate_first) v *= silu_f(to_f32<T>(gr[c]));
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    const float sg = silu_f(to_f32<T>(gr[c]));
+    const float wv = to_f32<T>(w[(c0 + c) % wlen]);
+    const float v = gate_first ? yr[c] * sg * inv * wv : yr[c] * inv * wv * sg;
+    out[(long long)t * C + c0 + c] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_act_rows_kernel(const T* __restrict__ in, T* __restrict__ out, long long total, int F, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long r = i / F;
+  const int c = (int)(i % F);
+  const float gte = to_f32<T>(in[r * 2 * F + c]), up = to_f32<T>(in[r * 2 * F + F + c]);
+  float a;
+  if (act == 2) {
+    a = 0.5f * gte * (1.f + tanhf(0.7978845608028654f * (gte + 0.044715f * gte * gte * gte)));
+  } else if (act == 3) {
+    a = silu_f(gte);
+  } else if (act == 1) {
+    a = fmaxf(gte, 0.f);
+  } else {
+    a = gte;
+  }
+  out[i] = from_f32<T>(a * up);
+}
+
+}  // namespace seqmix
+}  // namespace sxb
+
+using namespace sxb;
+using namespace sxb::seqmix;
+
+/* out fp32 [n_tokens, width] = table[ids[t]] * scale + p, p[2i] = sin(pos * base^(-2i/width)), p[2i+1] = cos(same).
+ * table: `dtype` [vocab, width]. */
+SXB_API int sxb_embed_sinusoid(const void* ids, const void* pos, const void* table, void* out, int n_tokens, int width,
+                               float scale, float base, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (embed_sinusoid_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+                             (const int*)ids, (const int*)pos, (const T*)table, (float*)out, width, scale, base)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Per row of the fp32 residual [rows, width]: if y: residual += y / rms(y) * w_post; if extra (fp32): residual += extra;
+ * if w_pre: out = residual / rms(residual) * w_pre.  y, w_post, w_pre, out are `dtype`; any of the three parts may be
+ * absent (null). */
+SXB_API int sxb_resid_norm_step(void* resid, const void* y, const void* w_post, const void* extra, const void* w_pre,
+                                void* out, long long rows, int width, float eps, int dtype, void* stream) {
+  if (rows <= 0) return SXB_OK;
+  if ((y == nullptr) != (w_post == nullptr) || (w_pre == nullptr) != (out == nullptr)) return SXB_ERR_BAD_ARG;
+  SEQMIX_DISPATCH(dtype, (resid_norm_step_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+                             (float*)resid, (const T*)y, (const T*)w_post, (const float*)extra, (const T*)w_pre,
+                             (T*)out, width, eps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Fused projection rows qkv [n_tokens, ld] = [Hq*d | G*d | G*dv] (+ bias): q and k heads divided by their root mean
+ * square (normalize != 0), q -> q_out fp32 [n_tokens, Hq, d], k -> kcache [pages, block_size, G, d], v -> vcache
+ * [pages, block_size, G, dv] at each token's (page, offset). */
+SXB_API int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, void* q_out, void* kcache, void* vcache,
+                               const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
+                               int max_blocks, int block_size, int Hq, int G, int d, int dv, float eps, int normalize,
+                               int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (qk_norm_append_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
+                             (const T*)qkv, ld, (const T*)bias, (float*)q_out, (T*)kcache, (T*)vcache,
+                             (const int*)tok_seq, (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq,
+                             G, d, dv, eps, normalize)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Attention of every token over the cached keys lo..pos of its sequence (lo = start of its chunk of `chunk` positions,
+ * or 0 when chunk == 0), scores and weights in fp32; sink (fp32 [Hq] or null) adds exp(sink[h]) to the denominator.
+ * out `dtype` [n_tokens, Hq * dv]. */
+SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
+                               const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
+                               int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
+                               int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (dv > 32 * kMaxVPerLane || Hq % G) return SXB_ERR_UNSUPPORTED;
+  const int warps = 4;
+  dim3 grid(n_tokens, (Hq + warps - 1) / warps);
+  SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, warps * 32, warps * d * sizeof(float), (cudaStream_t)stream>>>(
+                             (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out,
+                             (const int*)tok_seq, (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq,
+                             G, d, dv, scale, chunk)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Short causal filter + SiLU over C channels of x [n_tokens, ld] (`dtype`), w [C, taps] (last tap = current token),
+ * bias [C] or null, carried inputs state [slots, taps-1, C]; out fp32 [n_tokens, C].  seq_info int32 [n_seqs, 4] =
+ * {first row, rows, seen tokens, slot}. */
+SXB_API int sxb_conv_silu(const void* x, long long ld, const void* w, const void* bias, const void* state,
+                          const void* seq_info, const void* tok_seq, void* out, int n_tokens, int C, int taps,
+                          int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (taps < 1 || taps > kMaxTaps) return SXB_ERR_UNSUPPORTED;
+  dim3 grid(n_tokens, (C + 1023) / 1024);
+  SEQMIX_DISPATCH(dtype, (conv_silu_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)x, ld, (const T*)w, (const T*)bias, (const T*)state, (const int*)seq_info,
+                             (const int*)tok_seq, (float*)out, C, taps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Run after sxb_conv_silu on the same batch: every sequence's slot keeps its last taps-1 inputs. */
+SXB_API int sxb_conv_state_update(const void* x, long long ld, void* state, const void* seq_info, int n_seqs, int C,
+                                  int taps, int dtype, void* stream) {
+  if (n_seqs <= 0 || taps <= 1) return SXB_OK;
+  if (taps > kMaxTaps) return SXB_ERR_UNSUPPORTED;
+  dim3 grid(n_seqs, (C + 255) / 256);
+  SEQMIX_DISPATCH(dtype, (conv_state_update_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)x, ld, (T*)state, (const int*)seq_info, C, taps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* In place on fp32 rows x [n_tokens, ld]: heads of `dim` channels starting at col0 become x * mult / sqrt(sum x^2 + eps). */
+SXB_API int sxb_unit_norm_heads(void* x, long long ld, int col0, int n_heads, int dim, float mult, float eps,
+                                int n_tokens, void* stream) {
+  if (n_tokens <= 0 || n_heads <= 0) return SXB_OK;
+  const int total = n_tokens * n_heads;
+  unit_norm_heads_kernel<<<(total + 3) / 4, 128, 0, (cudaStream_t)stream>>>((float*)x, ld, col0, n_heads, dim, mult, eps,
+                                                                           n_tokens);
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* decay, beta fp32 [n_tokens, H] from raw projections (`dtype`, row pitch ld, H channels each), A_log / dt_bias fp32 [H].
+ * mode 0: beta = sigmoid(b_raw), decay = exp(-exp(A_log) softplus(a_raw + dt_bias)).
+ * mode 1: beta = softplus(a_raw + dt_bias) (b_raw unused), decay = exp(-exp(A_log) beta). */
+SXB_API int sxb_recurrence_gates(const void* a_raw, const void* b_raw, long long ld, const void* A_log,
+                                 const void* dt_bias, void* decay, void* beta, int H, int n_tokens, int mode, int dtype,
+                                 void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  const int total = n_tokens * H;
+  SEQMIX_DISPATCH(dtype, (recurrence_gates_kernel<T><<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)a_raw, (const T*)b_raw, ld, (const float*)A_log, (const float*)dt_bias,
+                             (float*)decay, (float*)beta, H, n_tokens, mode)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Per sequence and head, rows in order:  S <- decay S;  u = beta (v - [delta] S^T k);  S <- S + k u^T;
+ * o = S^T q (+ skip[h] v).  kvec / qvec fp32 [rows, ldkq] hold G heads of n channels, val fp32 [rows, ldv] H heads of dv,
+ * decay / beta fp32 [rows, H], state fp32 [slots, H, dv, n] (taken as zero when the sequence has seen no token), out fp32
+ * [rows, H * dv]. */
+SXB_API int sxb_linear_recurrence(const void* kvec, const void* qvec, long long ldkq, const void* val, long long ldv,
+                                  const void* decay, const void* beta, const void* skip, void* state, void* out,
+                                  const void* seq_info, int n_seqs, int H, int G, int n, int dv, int delta,
+                                  void* stream) {
+  if (n_seqs <= 0) return SXB_OK;
+  if (n > 256 || H % G) return SXB_ERR_UNSUPPORTED;
+  dim3 grid((dv + kCols - 1) / kCols, H, n_seqs);
+  const size_t smem = (size_t)(2 * kTB * n + kTB * kCols + 2 * kTB) * sizeof(float);
+  cudaStream_t s = (cudaStream_t)stream;
+#define LAUNCH_REC(R)                                                                                              \
+  linear_recurrence_kernel<R><<<grid, kLPC * kCols, smem, s>>>(                                                     \
+      (const float*)kvec, (const float*)qvec, ldkq, (const float*)val, ldv, (const float*)decay, (const float*)beta, \
+      (const float*)skip, (float*)state, (float*)out, (const int*)seq_info, H, G, n, dv, delta)
+  if (n <= 32) LAUNCH_REC(4);
+  else if (n <= 64) LAUNCH_REC(8);
+  else if (n <= 128) LAUNCH_REC(16);
+  else LAUNCH_REC(32);
+#undef LAUNCH_REC
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* RMS norm over groups of gs channels of y fp32 [n_tokens, C] with a SiLU gate (`dtype` rows of pitch ldg) and a weight
+ * of wlen entries that repeats along the row.  gate_first: norm(y silu(gate)) w; else norm(y) w silu(gate). */
+SXB_API int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, const void* w, int wlen, void* out,
+                                int n_tokens, int C, int gs, float eps, int gate_first, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (gs <= 0 || C % gs) return SXB_ERR_BAD_ARG;
+  dim3 grid(n_tokens, C / gs);
+  SEQMIX_DISPATCH(dtype, (group_norm_gate_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+                             (const float*)y, (const T*)gate, ldg, (const T*)w, wlen, (T*)out, C, gs, eps, gate_first)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out [rows, F] = act(in[:, :F]) * in[:, F:] for rows of any width; act: 0 identity, 1 relu, 2 gelu (tanh form), 3 silu. */
+SXB_API int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, void* stream) {
+  const long long total = rows * F;
+  if (total <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (gated_act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)in, (T*)out, total, F, act)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}

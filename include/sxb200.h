@@ -446,6 +446,36 @@ int sxbh_fill_ragged_batch(int32_t* tok_seq, int32_t* tok_pos, int32_t* last_tok
 int sxb_int_gemv(const void* x, const void* codes, const void* scale, const void* minv, void* y, int M, int N,
                  int K, int bits, int group_size, long long x_stride, long long y_stride, void* stream);
 
+/* ---- csrc/seq_mixers.cu */
+int sxb_embed_sinusoid(const void* ids, const void* pos, const void* table, void* out, int n_tokens, int width,
+                       float scale, float base, int dtype, void* stream);
+int sxb_resid_norm_step(void* resid, const void* y, const void* w_post, const void* extra, const void* w_pre,
+                        void* out, long long rows, int width, float eps, int dtype, void* stream);
+int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, void* q_out, void* kcache, void* vcache,
+                       const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens, int max_blocks,
+                       int block_size, int Hq, int G, int d, int dv, float eps, int normalize, int dtype,
+                       void* stream);
+int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
+                       const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens, int max_blocks,
+                       int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int dtype,
+                       void* stream);
+int sxb_conv_silu(const void* x, long long ld, const void* w, const void* bias, const void* state,
+                  const void* seq_info, const void* tok_seq, void* out, int n_tokens, int C, int taps, int dtype,
+                  void* stream);
+int sxb_conv_state_update(const void* x, long long ld, void* state, const void* seq_info, int n_seqs, int C,
+                          int taps, int dtype, void* stream);
+int sxb_unit_norm_heads(void* x, long long ld, int col0, int n_heads, int dim, float mult, float eps, int n_tokens,
+                        void* stream);
+int sxb_recurrence_gates(const void* a_raw, const void* b_raw, long long ld, const void* A_log,
+                         const void* dt_bias, void* decay, void* beta, int H, int n_tokens, int mode, int dtype,
+                         void* stream);
+int sxb_linear_recurrence(const void* kvec, const void* qvec, long long ldkq, const void* val, long long ldv,
+                          const void* decay, const void* beta, const void* skip, void* state, void* out,
+                          const void* seq_info, int n_seqs, int H, int G, int n, int dv, int delta, void* stream);
+int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, const void* w, int wlen, void* out,
+                        int n_tokens, int C, int gs, float eps, int gate_first, int dtype, void* stream);
+int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,18 @@ from ..logging import inference_logger
 from .base_engine import CheckpointEngineBase
 
 
+class PlainModelConfig:
+    """``config.json`` as data: ``model_type`` is the lower-cased ``"architecture"``, ``raw`` the whole object."""
+
+    def __init__(self, raw: dict) -> None:
+        self.raw = raw
+        self.model_type = str(raw["architecture"]).lower()
+        self.torch_dtype = None
+
+    def to_dict(self) -> dict:
+        return dict(self.raw)
+
+
 class HuggingFaceCheckpointEngine(CheckpointEngineBase):
 
     def __init__(self, model_name_or_path: str, auth_token: str = None, **hf_kwargs) -> None:
@@ -21,12 +33,16 @@ class HuggingFaceCheckpointEngine(CheckpointEngineBase):
         self.auth_token = auth_token
         if not os.path.isdir(model_name_or_path):
             raise ValueError(f"{model_name_or_path} is not a local directory; hub downloads are unavailable offline")
-        from transformers import AutoConfig, GenerationConfig
-        self.model_config = AutoConfig.from_pretrained(model_name_or_path, **hf_kwargs)
-        try:
-            self.generation_config = GenerationConfig.from_pretrained(model_name_or_path)
-        except Exception:
-            self.generation_config = None
+        plain = self._plain_config(model_name_or_path)
+        if plain is not None:
+            self.model_config, self.generation_config = plain, None
+        else:
+            from transformers import AutoConfig, GenerationConfig
+            self.model_config = AutoConfig.from_pretrained(model_name_or_path, **hf_kwargs)
+            try:
+                self.generation_config = GenerationConfig.from_pretrained(model_name_or_path)
+            except Exception:
+                self.generation_config = None
         if not hasattr(self.model_config, "max_seq_length"):
             for k in ("max_position_embeddings", "n_positions", "seq_length"):
                 if hasattr(self.model_config, k):
@@ -36,6 +52,19 @@ class HuggingFaceCheckpointEngine(CheckpointEngineBase):
                 self.model_config.max_seq_length = 2048
         self._local_checkpoint_dir = model_name_or_path
         self._all_ckpt_paths = self._fetch_checkpoint_files()
+
+    @staticmethod
+    def _plain_config(path: str):
+        """Checkpoints of architectures that are not in the transformers library name themselves by an
+        ``"architecture"`` key in ``config.json`` (no ``"model_type"``); their config is the JSON object itself."""
+        fn = os.path.join(path, "config.json")
+        if not os.path.isfile(fn):
+            return None
+        with open(fn) as f:
+            raw = json.load(f)
+        if "model_type" in raw or "architecture" not in raw:
+            return None
+        return PlainModelConfig(raw)
 
     def _fetch_checkpoint_files(self) -> List[str]:
         d = self._local_checkpoint_dir

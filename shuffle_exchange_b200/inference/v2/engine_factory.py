@@ -61,9 +61,10 @@ def build_engine_from_ds_checkpoint(path: str, engine_config: RaggedInferenceEng
 
 
 def build_hf_engine(path: str, engine_config: RaggedInferenceEngineConfig = None,
-                    debug_level: int = logging.INFO) -> InferenceEngineV2:
+                    debug_level: int = logging.INFO, dtype: torch.dtype = None, device=None) -> InferenceEngineV2:
     """Engine for a local HuggingFace checkpoint directory (or a serialized v2 checkpoint) of a supported
-    architecture: llama, mistral, mixtral, falcon, opt, phi, phi3, qwen, qwen2, qwen2_moe."""
+    architecture: llama, mistral, mixtral, falcon, opt, phi, phi3, qwen, qwen2, qwen2_moe, fomalix.  ``dtype`` overrides
+    the checkpoint's activation dtype (``torch.float32`` evaluates a model in full precision where it supports that)."""
     engine_config = engine_config or RaggedInferenceEngineConfig()
     if os.path.exists(os.path.join(path, "ds_model_config.pkl")):
         return build_engine_from_ds_checkpoint(path, engine_config, debug_level=debug_level)
@@ -71,4 +72,6 @@ def build_hf_engine(path: str, engine_config: RaggedInferenceEngineConfig = None
     ce = HuggingFaceCheckpointEngine(path)
     policy = _policy_for(ce.model_config, ce)
     policy._engine_config = engine_config
-    return InferenceEngineV2(policy, engine_config)
+    if dtype is not None:
+        policy.dtype_override = dtype
+    return InferenceEngineV2(policy, engine_config, device=device)

@@ -33,8 +33,9 @@ class InferenceEngineV2:
             builder = lambda sm: RaggedLlamaModel(policy_or_model, sm)
         probe = builder(None)
         kv_cfg = probe.kv_cache_config(self._config.kv_block_size)
+        state_cfg = probe.state_pool_config() if hasattr(probe, "state_pool_config") else None
         self._state_manager = DSStateManager(self._config.state_manager, kv_cfg, device=device,
-                                             mp_group=self._base_mp_group)
+                                             mp_group=self._base_mp_group, state_config=state_cfg)
         self._model = builder(self._state_manager)
         sm = self._config.state_manager
         self._batch = RaggedBatchWrapper(sm.max_ragged_batch_size, sm.max_ragged_sequence_count,
@@ -65,21 +66,27 @@ class InferenceEngineV2:
     def model(self):
         return self._model
 
-    def put(self, batch_uids: Iterable[int], batch_tokens: Iterable[torch.Tensor], do_checks: bool = True) -> torch.Tensor:
+    def put(self, batch_uids: Iterable[int], batch_tokens: Iterable[torch.Tensor], do_checks: bool = True,
+            logit_positions=None) -> torch.Tensor:
+        """One forward over the given sequences' next tokens.  Returns the logits of every sequence's last token,
+        ``[n_seqs, vocab]``; with ``logit_positions`` (per sequence a list of indices among its tokens, possibly empty)
+        the logits of exactly those tokens, in batch order."""
         batch_uids, batch_tokens = list(batch_uids), list(batch_tokens)
+        if logit_positions is None:
+            logit_positions = [None] * len(batch_uids)
         if do_checks:
             res = self.can_schedule(batch_uids, [t.numel() for t in batch_tokens])
             if res != SchedulingResult.Success:
                 raise SchedulingError(res)
         self._batch.clear()
         seqs = []
-        for uid, tokens in zip(batch_uids, batch_tokens):
+        for uid, tokens, rows in zip(batch_uids, batch_tokens, logit_positions):
             seq = self._state_manager.get_or_create_sequence(uid)
             if seq.is_offloaded:
                 self._state_manager.restore_sequence(uid)
             self._model.maybe_allocate_kv(seq, tokens.numel())
             seq.pre_forward(tokens.numel())
-            self._batch.insert_sequence(seq, tokens.reshape(-1).cpu(), do_checks=do_checks)
+            self._batch.insert_sequence(seq, tokens.reshape(-1).cpu(), do_checks=do_checks, logit_rows=rows)
             seqs.append(seq)
         self._batch.finalize()
         logits = self._model.forward(self._batch)

@@ -272,6 +272,8 @@ class FalconNewArchContainerPolicy(ContainerPolicyMixin, FalconPolicy):
 CONTAINER_POLICIES = {"llama": Llama2ContainerPolicy, "mistral": Llama2ContainerPolicy, "qwen2": Llama2ContainerPolicy,
                       "mixtral": MixtralContainerPolicy, "opt": OPTContainerPolicy}
 
-POLICIES = {"llama": Llama2Policy, "mistral": MistralPolicy, "mixtral": MixtralPolicy, "falcon": FalconPolicy,
+from .fomalix import FomalixPolicy  # noqa: E402
+
+POLICIES = {"fomalix": FomalixPolicy, "llama": Llama2Policy, "mistral": MistralPolicy, "mixtral": MixtralPolicy, "falcon": FalconPolicy,
             "opt": OPTPolicy, "phi": PhiPolicy, "phi3": Phi3Policy, "qwen": QwenPolicy, "qwen2": Qwen2Policy,
             "qwen2_moe": Qwen2MoePolicy}

@@ -26,6 +26,7 @@ class MaskingType(Enum):
     local = "local"
     symmetric = "symmetric"
     asymmetric = "asymmetric"
+    chunked = "chunked"      # causal inside aligned chunks of ``masking_args["size"]`` positions, nothing across chunks
 
 
 class DSSelfAttentionConfig(DSModuleConfig):
@@ -40,6 +41,10 @@ class DSSelfAttentionConfig(DSModuleConfig):
     masking_args: Dict = {}
     positional_embedding_type: PositionalEmbeddingType = PositionalEmbeddingType.none
     positional_embedding_config: Optional[RotateHalfConfig] = None
+    v_head_size: Optional[int] = None     # value head size when it differs from the query / key head size
+    qk_unit_rms: bool = False             # divide every query / key head by its root mean square (no weight)
+    qk_norm_eps: float = 1e-5
+    sink: bool = False                    # one learned logit per head joins the softmax denominator
 
 
 class DSEmbeddingsConfig(DSModuleConfig):
@@ -49,6 +54,8 @@ class DSEmbeddingsConfig(DSModuleConfig):
     positional_offset: int = 0            # OPT stores position p at row p + 2
     use_token_type: bool = False
     output_normalization: Optional[NormTypeEnum] = None
+    scale: float = 1.0                    # multiplies the token rows
+    sinusoid_base: Optional[float] = None  # adds interleaved sin / cos of pos * base^(-2i/dim) when set
 
 
 class DSLinearConfig(DSModuleConfig):
@@ -86,3 +93,24 @@ class DSUnembedConfig(DSModuleConfig):
     max_sequences: int
     vocab_size: int
     eps: float = 1e-5
+
+
+class DSRecurrentMixerConfig(DSModuleConfig):
+    """A token mixer that carries a matrix state per head instead of a key / value cache.
+
+    ``kind`` ``"delta"``: gated delta rule (keys / queries of ``key_dim`` channels shared by ``n_heads // n_heads_kv``
+    value heads, short convolutions on q, k, v).  ``"ssd"``: state-space duality (B / C of ``key_dim`` = state size per
+    group, a convolution over x | B | C, a skip term and a gated group norm)."""
+    kind: str
+    model_dim: int
+    n_heads: int
+    n_heads_kv: int                       # key/query heads (delta) or B/C groups (ssd)
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_groups: int = 1
+    eps: float = 1e-5
+    unit_norm_eps: float = 1e-6
+    max_sequences: int = 1
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16

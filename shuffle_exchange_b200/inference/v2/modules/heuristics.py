@@ -4,22 +4,26 @@ from __future__ import annotations
 from ..config_v2 import RaggedInferenceEngineConfig
 from ..inference_utils import NormTypeEnum
 from . import implementations  # noqa: F401  (registers the implementations)
-from .configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSSelfAttentionConfig,
-                      DSUnembedConfig)
+from .configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSRecurrentMixerConfig,
+                      DSSelfAttentionConfig, DSUnembedConfig)
 from .interfaces import (DSEmbeddingBase, DSEmbeddingRegistry, DSLinearBase, DSLinearRegistry, DSMoEBase,
                          DSMoERegistry, DSPostNormBase, DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry,
-                         DSSelfAttentionBase, DSSelfAttentionRegistry, DSUnembedBase, DSUnembedRegistry)
+                         DSRecurrentMixerBase, DSRecurrentMixerRegistry, DSSelfAttentionBase, DSSelfAttentionRegistry,
+                         DSUnembedBase, DSUnembedRegistry)
 from .module_registry import ConfigBundle
 
 
 def instantiate_attention(attention_config: DSSelfAttentionConfig,
                           engine_config: RaggedInferenceEngineConfig) -> DSSelfAttentionBase:
-    return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="dense_blocked_attention",
-                                                                   config=attention_config))
+    name = "dense_blocked_attention"
+    if not DSSelfAttentionRegistry.registry[name].supports_config(attention_config):
+        name = "sink_chunked_attention"       # chunk-local mask, sink logit, q/k unit norm or narrower value heads
+    return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name=name, config=attention_config))
 
 
 def instantiate_embed(embed_config: DSEmbeddingsConfig, engine_config: RaggedInferenceEngineConfig) -> DSEmbeddingBase:
-    return DSEmbeddingRegistry.instantiate_config(ConfigBundle(name="ragged_embedding", config=embed_config))
+    name = "ragged_embedding" if embed_config.sinusoid_base is None else "scaled_sinusoid_embedding"
+    return DSEmbeddingRegistry.instantiate_config(ConfigBundle(name=name, config=embed_config))
 
 
 def instantiate_linear(linear_config: DSLinearConfig, engine_config: RaggedInferenceEngineConfig) -> DSLinearBase:
@@ -52,3 +56,16 @@ def instantiate_pre_norm(norm_config: DSNormConfig, engine_config: RaggedInferen
 
 def instantiate_unembed(unembed_config: DSUnembedConfig, engine_config: RaggedInferenceEngineConfig) -> DSUnembedBase:
     return DSUnembedRegistry.instantiate_config(ConfigBundle(name="ragged_unembed", config=unembed_config))
+
+
+def instantiate_recurrent_mixer(mixer_config: DSRecurrentMixerConfig,
+                                engine_config: RaggedInferenceEngineConfig) -> DSRecurrentMixerBase:
+    name = {"delta": "gated_delta_mixer", "ssd": "ssd_mixer"}.get(mixer_config.kind)
+    if name is None:
+        raise ValueError(f"Unknown recurrent mixer kind {mixer_config.kind!r}; expected 'delta' or 'ssd'")
+    return DSRecurrentMixerRegistry.instantiate_config(ConfigBundle(name=name, config=mixer_config))
+
+
+def instantiate_sandwich_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig) -> DSPreNormBase:
+    """Pre- and post-norm around every sublayer on an fp32 residual stream."""
+    return DSPreNormRegistry.instantiate_config(ConfigBundle(name="fp32_sandwich_rms", config=norm_config))

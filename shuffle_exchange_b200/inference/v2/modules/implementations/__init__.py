@@ -9,6 +9,12 @@
  ``cutlass_multi_gemm_moe``   top-k gating / scatter / per-expert GEMMs over contiguous row ranges / weighted gather
  ``cuda_pre_ln / cuda_pre_rms / cuda_post_ln``   fused residual-add + norm kernels
  ``ragged_unembed``           (norm +) last-token gather + vocabulary GEMM
+ ``sink_chunked_attention``   bias + unit-RMS q/k + cache append (``sxb_qk_norm_append``), causal or chunk-local softmax
+                              with a sink logit over the paged cache in fp32 (``sxb_sink_attention``)
+ ``scaled_sinusoid_embedding``  token row * scale + sinusoidal position vector into an fp32 residual
+ ``fp32_sandwich_rms``        fp32 residual += post-norm(sublayer output); next pre-norm, one kernel
+ ``gated_delta_mixer`` / ``ssd_mixer``   short convolutions with carried inputs + linear recurrence with a matrix
+                              state per (sequence slot, head) + gated group norm
 =========================  =======================================================================================
 """
 from __future__ import annotations
@@ -23,11 +29,13 @@ from .....ops import moe_ops
 from ...inference_parameter import InferenceParameter
 from ...inference_utils import ActivationType, DtypeEnum, NormTypeEnum, is_gated
 from ...kernels import ragged_ops as R
-from ..configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSSelfAttentionConfig,
-                       DSUnembedConfig, MaskingType, PositionalEmbeddingType)
+from ...kernels import mixer_ops as M
+from ..configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSRecurrentMixerConfig,
+                       DSSelfAttentionConfig, DSUnembedConfig, MaskingType, PositionalEmbeddingType)
 from ..interfaces import (DSEmbeddingBase, DSEmbeddingRegistry, DSLinearBase, DSLinearRegistry, DSMoEBase,
                           DSMoERegistry, DSPostNormBase, DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry,
-                          DSSelfAttentionBase, DSSelfAttentionRegistry, DSUnembedBase, DSUnembedRegistry, _param)
+                          DSRecurrentMixerBase, DSRecurrentMixerRegistry, DSSelfAttentionBase, DSSelfAttentionRegistry,
+                          DSUnembedBase, DSUnembedRegistry, _param)
 
 
 def _dt(x) -> DtypeEnum:
@@ -64,6 +72,8 @@ class DSDenseBlockedAttention(DSSelfAttentionBase):
     @staticmethod
     def supports_config(config: DSSelfAttentionConfig) -> bool:
         if MaskingType(config.masking_type) != MaskingType.causal:
+            return False
+        if config.sink or config.qk_unit_rms or config.v_head_size not in (None, config.head_size):
             return False
         return PositionalEmbeddingType(config.positional_embedding_type) in (PositionalEmbeddingType.none,
                                                                              PositionalEmbeddingType.rotate_half)
@@ -105,7 +115,8 @@ class DSRaggedEmbedding(DSEmbeddingBase):
 
     @staticmethod
     def supports_config(config: DSEmbeddingsConfig) -> bool:
-        return not config.use_token_type and config.output_normalization is None
+        return (not config.use_token_type and config.output_normalization is None and config.sinusoid_base is None
+                and config.scale == 1.0)
 
     def __init__(self, config, implementation_config):
         super().__init__(config, implementation_config)
@@ -340,3 +351,196 @@ class DSRaggedUnembed(DSUnembedBase):
         logits = F.linear(last, vocab_embedding)
         self._output = logits if bias is None else logits + bias
         return self._output
+
+
+# ============================================================================================ hybrid stacks
+@DSSelfAttentionRegistry.register_module
+class DSSinkChunkedAttention(DSSelfAttentionBase):
+    """Attention without rotation whose value heads may be narrower than its key heads: optional per-head unit-RMS
+    of q and k, causal or chunk-local mask, optional sink logit in the softmax denominator.  Scores, weights and the
+    weighted sum are fp32; the paged cache is a ``(keys, values)`` pair in the activation dtype."""
+
+    @staticmethod
+    def name() -> str:
+        return "sink_chunked_attention"
+
+    @staticmethod
+    def supports_config(config: DSSelfAttentionConfig) -> bool:
+        if MaskingType(config.masking_type) not in (MaskingType.causal, MaskingType.chunked):
+            return False
+        if MaskingType(config.masking_type) == MaskingType.chunked and int(config.masking_args.get("size", 0)) < 1:
+            return False
+        return (PositionalEmbeddingType(config.positional_embedding_type) == PositionalEmbeddingType.none
+                and (config.v_head_size or config.head_size) <= 256 and config.n_heads_q % config.n_heads_kv == 0)
+
+    @property
+    def kv_block_size(self) -> int:
+        return 64
+
+    @property
+    def q_block_size(self) -> int:
+        return 1
+
+    def forward(self, q_k_v: torch.Tensor, kv_cache, batch, inv_freqs=None, bias=None, sink=None) -> torch.Tensor:
+        c = self._config
+        dv = c.v_head_size or c.head_size
+        chunk = int(c.masking_args["size"]) if MaskingType(c.masking_type) == MaskingType.chunked else 0
+        keys, values = kv_cache
+        t2s, pos, tables = batch.token_to_seq(), batch.token_positions(), batch.block_tables()
+        q = M.qk_norm_append(q_k_v, bias, keys, values, t2s, pos, tables, c.n_heads_q, c.n_heads_kv, c.head_size, dv,
+                             c.qk_norm_eps, c.qk_unit_rms)
+        return M.sink_attention(q, keys, values, sink if c.sink else None, t2s, pos, tables, c.scale_factor, chunk,
+                                _dt(c.output_dtype).torch)
+
+
+@DSEmbeddingRegistry.register_module
+class DSScaledSinusoidEmbedding(DSEmbeddingBase):
+
+    @staticmethod
+    def name() -> str:
+        return "scaled_sinusoid_embedding"
+
+    @staticmethod
+    def supports_config(config: DSEmbeddingsConfig) -> bool:
+        return (config.sinusoid_base is not None and not config.use_token_type and not config.positional_embedding
+                and _dt(config.residual_dtype) == DtypeEnum.fp32)
+
+    def __init__(self, config, implementation_config):
+        super().__init__(config, implementation_config)
+        self._output = None
+
+    @property
+    def output(self) -> torch.Tensor:
+        return self._output
+
+    def forward(self, ragged_batch, word_embeddings, position_embeddings=None, token_type_ids=None,
+                token_type_embeddings=None) -> torch.Tensor:
+        c = self._config
+        self._output = M.embed_sinusoid(ragged_batch.input_ids(), ragged_batch.token_positions(), word_embeddings,
+                                        c.scale, c.sinusoid_base)
+        return self._output
+
+
+@DSPreNormRegistry.register_module
+class DSSandwichRMSNorm(DSPreNormBase):
+    """Layers of the form ``x <- x + post_norm(sublayer(pre_norm(x)))`` on an fp32 residual: one kernel closes the
+    previous sublayer (``residual += rms_norm(hidden) * gamma_post``), optionally adds another fp32 stream, and opens the
+    next one (returns ``rms_norm(residual) * gamma``)."""
+
+    @staticmethod
+    def name() -> str:
+        return "fp32_sandwich_rms"
+
+    @staticmethod
+    def supports_config(config: DSNormConfig) -> bool:
+        return NormTypeEnum(config.type) == NormTypeEnum.RMSNorm and _dt(config.residual_dtype) == DtypeEnum.fp32
+
+    def forward(self, residual, hidden_states, gamma, beta=None, gamma_post=None, extra=None):
+        y = M.resid_norm_step(residual, hidden_states, gamma_post, extra, gamma, self._config.eps,
+                              _dt(self._config.output_dtype).torch)
+        return residual, y
+
+
+class _RecurrentMixer(DSRecurrentMixerBase):
+
+    def __init__(self, config, implementation_config):
+        super().__init__(config, implementation_config)
+
+    @property
+    def conv_channels(self) -> int:
+        raise NotImplementedError
+
+    def state_shapes(self):
+        """[(shape per sequence, dtype)]: the convolution's carried inputs, then the matrix state of every head."""
+        c = self._config
+        return [((c.conv_taps - 1, self.conv_channels), _dt(c.input_dtype).torch),
+                ((c.n_heads, c.value_dim, c.key_dim), torch.float32)]
+
+
+@DSRecurrentMixerRegistry.register_module
+class DSGatedDeltaMixer(_RecurrentMixer):
+    """Gated delta rule.  Projection columns: ``q (G n) | k (G n) | v (H dv) | gate (H dv) | b (H) | a (H)``; q, k, v pass
+    a short convolution + SiLU, q and k become unit vectors (q also times ``n^-1/2``), ``beta = sigmoid(b)``,
+    ``decay = exp(-exp(A_log) softplus(a + dt_bias))``; per head ``S <- decay S; S <- S + k (beta (v - S^T k))^T;
+    o = S^T q``; the output is ``rms_norm(o) * norm * silu(gate)`` per head."""
+
+    @staticmethod
+    def name() -> str:
+        return "gated_delta_mixer"
+
+    @staticmethod
+    def supports_config(config: DSRecurrentMixerConfig) -> bool:
+        return (config.kind == "delta" and config.key_dim <= 256 and 1 <= config.conv_taps <= 16
+                and config.n_heads % config.n_heads_kv == 0)
+
+    @property
+    def conv_channels(self) -> int:
+        c = self._config
+        return 2 * c.n_heads_kv * c.key_dim + c.n_heads * c.value_dim
+
+    @property
+    def projection_width(self) -> int:
+        c = self._config
+        return self.conv_channels + c.n_heads * c.value_dim + 2 * c.n_heads
+
+    def forward(self, projected, weights, states, batch):
+        c = self._config
+        H, G, n, dv = c.n_heads, c.n_heads_kv, c.key_dim, c.value_dim
+        C = self.conv_channels
+        conv_state, S = states
+        info, t2s = batch.seq_info(), batch.token_to_seq()
+        xin = projected[:, :C]
+        x = M.conv_silu(xin, weights.conv_w, None, conv_state, info, t2s)
+        M.conv_state_update(xin, conv_state, info)
+        M.unit_norm_heads(x, 0, G, n, n ** -0.5, c.unit_norm_eps)
+        M.unit_norm_heads(x, G * n, G, n, 1.0, c.unit_norm_eps)
+        g0 = C + H * dv
+        decay, beta = M.recurrence_gates(projected[:, g0 + H: g0 + 2 * H], projected[:, g0: g0 + H], weights.A_log,
+                                         weights.dt_bias, "delta")
+        o = M.linear_recurrence(x[:, G * n: 2 * G * n], x[:, : G * n], x[:, 2 * G * n:], decay, beta, None, S, info, H, G,
+                                n, dv, True)
+        return M.group_norm_gate(o, projected[:, C: C + H * dv], weights.norm, dv, c.eps, False,
+                                 _dt(c.output_dtype).torch)
+
+
+@DSRecurrentMixerRegistry.register_module
+class DSStateSpaceDualMixer(_RecurrentMixer):
+    """State-space duality.  Projection columns: ``z (H dv) | x (H dv) | B (G n) | C (G n) | dt (H)``; x | B | C pass one
+    short convolution (with bias) + SiLU; ``dt = softplus(dt + dt_bias)``; per head ``S <- exp(-exp(A_log) dt) S +
+    dt B x^T; y = S^T C + D x``; the output is ``rms_norm(y * silu(z))`` over ``norm_groups`` equal parts times ``norm``."""
+
+    @staticmethod
+    def name() -> str:
+        return "ssd_mixer"
+
+    @staticmethod
+    def supports_config(config: DSRecurrentMixerConfig) -> bool:
+        inner = config.n_heads * config.value_dim
+        return (config.kind == "ssd" and config.key_dim <= 256 and 1 <= config.conv_taps <= 16
+                and config.n_heads % config.n_heads_kv == 0 and inner % config.norm_groups == 0)
+
+    @property
+    def conv_channels(self) -> int:
+        c = self._config
+        return c.n_heads * c.value_dim + 2 * c.n_heads_kv * c.key_dim
+
+    @property
+    def projection_width(self) -> int:
+        c = self._config
+        return c.n_heads * c.value_dim + self.conv_channels + c.n_heads
+
+    def forward(self, projected, weights, states, batch):
+        c = self._config
+        H, G, n, dv = c.n_heads, c.n_heads_kv, c.key_dim, c.value_dim
+        inner, C = H * dv, self.conv_channels
+        conv_state, S = states
+        info, t2s = batch.seq_info(), batch.token_to_seq()
+        xin = projected[:, inner: inner + C]
+        x = M.conv_silu(xin, weights.conv_w, weights.conv_b, conv_state, info, t2s)
+        M.conv_state_update(xin, conv_state, info)
+        decay, dt = M.recurrence_gates(projected[:, inner + C: inner + C + H], None, weights.A_log, weights.dt_bias,
+                                       "ssd")
+        y = M.linear_recurrence(x[:, inner: inner + G * n], x[:, inner + G * n:], x[:, :inner], decay, dt, weights.D, S,
+                                info, H, G, n, dv, False)
+        return M.group_norm_gate(y, projected[:, :inner], weights.norm, inner // c.norm_groups, c.eps, True,
+                                 _dt(c.output_dtype).torch)

@@ -8,8 +8,8 @@ import torch
 
 from ...inference_parameter import InferenceParameter
 from ...ragged.ragged_wrapper import RaggedBatchWrapper
-from ..configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSSelfAttentionConfig,
-                       DSUnembedConfig)
+from ..configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSRecurrentMixerConfig,
+                       DSSelfAttentionConfig, DSUnembedConfig)
 from ..ds_module import DSModuleBase
 from ..module_registry import DSModuleRegistryBase
 
@@ -233,3 +233,34 @@ class DSUnembedRegistry(DSModuleRegistryBase):
     @staticmethod
     def associated_class() -> Type[DSModuleBase]:
         return DSUnembedBase
+
+
+# ------------------------------------------------------------------------------------------ recurrent mixers
+class DSRecurrentMixerBase(DSModuleBase):
+    """Ragged recurrent token mixer: ``forward(projected [tokens, proj_width], weights, states, batch) ->
+    [tokens, n_heads * value_dim]`` (the input of the output projection).  ``proj_width`` and the order of its column
+    blocks are the implementation's (``projection_layout``); ``state_shapes`` lists the per-sequence tensors it keeps in
+    the recurrent-state pool and ``states`` passes them back in that order."""
+
+    @staticmethod
+    def config_class() -> Type[DSRecurrentMixerConfig]:
+        return DSRecurrentMixerConfig
+
+    def __init__(self, config: DSRecurrentMixerConfig, implementation_config: Dict[str, Any]) -> None:
+        super().__init__(config, implementation_config)
+
+    @abstractmethod
+    def state_shapes(self):
+        ...
+
+    @abstractmethod
+    def forward(self, projected: torch.Tensor, weights, states, batch: RaggedBatchWrapper) -> torch.Tensor:
+        ...
+
+
+class DSRecurrentMixerRegistry(DSModuleRegistryBase):
+    registry: Dict = {}
+
+    @staticmethod
+    def associated_class() -> Type[DSModuleBase]:
+        return DSRecurrentMixerBase

@@ -1,6 +1,10 @@
 """Paged KV cache (reference: ``inference/v2/ragged/kv_cache.py:40-208``): one tensor
 ``[n_layers, n_blocks, block_size, 2, n_kv_heads, head_dim]`` per cache group + a :class:`BlockedAllocator`.  Sizing
-follows the reference's policy: either an explicit block count or "fill ``memory_fraction`` of free HBM"."""
+follows the reference's policy: either an explicit block count or "fill ``memory_fraction`` of free HBM".
+
+Models whose cached layers differ in shape, or whose keys and values differ in head size, describe every cached layer
+by ``KVCacheConfig.layer_shapes``; the cache then holds one key tensor ``[n_blocks, block_size, n_kv_heads, key_dim]`` and
+one value tensor ``[n_blocks, block_size, n_kv_heads, value_dim]`` per layer, all indexed by the same block ids."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -18,6 +22,7 @@ class KVCacheConfig:
     cache_shape: Tuple[int, int, int] = (1, 1, 1)        # (n_layers, n_kv_heads, head_dim)
     cache_dtype: torch.dtype = torch.bfloat16
     max_blocks_per_allocation_group: int = 64
+    layer_shapes: Optional[Tuple[Tuple[int, int, int], ...]] = None   # per cached layer (n_kv_heads, key_dim, value_dim)
 
 
 def split_kv(kv_cache: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -35,6 +40,8 @@ class BlockedKVCache:
         n_layers, n_kv, d = config.cache_shape
         elem = torch.tensor([], dtype=config.cache_dtype).element_size()
         per_block = n_layers * config.block_size * 2 * n_kv * d * elem
+        if config.layer_shapes is not None:
+            per_block = max(1, sum(config.block_size * g * (dk + dv) * elem for g, dk, dv in config.layer_shapes))
         dev = device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu")
         if num_blocks is None:
             if torch.device(dev).type == "cuda":
@@ -50,7 +57,15 @@ class BlockedKVCache:
                 dist.all_reduce(t, op=dist.ReduceOp.MIN, group=mp_group)
                 num_blocks = int(t.item())
         self._num_blocks = num_blocks
-        self._cache = torch.zeros(n_layers, num_blocks, config.block_size, 2, n_kv, d, dtype=config.cache_dtype, device=dev)
+        self._split = None
+        if config.layer_shapes is not None:
+            self._split = [(torch.zeros(num_blocks, config.block_size, g, dk, dtype=config.cache_dtype, device=dev),
+                            torch.zeros(num_blocks, config.block_size, g, dv, dtype=config.cache_dtype, device=dev))
+                           for g, dk, dv in config.layer_shapes]
+            self._cache = torch.zeros(0, dtype=config.cache_dtype, device=dev)
+        else:
+            self._cache = torch.zeros(n_layers, num_blocks, config.block_size, 2, n_kv, d, dtype=config.cache_dtype,
+                                      device=dev)
         self._allocator = BlockedAllocator(num_blocks)
 
     def reserve(self, num_blocks: int) -> torch.Tensor:
@@ -59,7 +74,11 @@ class BlockedKVCache:
     def free(self, blocks) -> None:
         self._allocator.free(blocks)
 
-    def get_cache(self, layer: int) -> torch.Tensor:
+    def get_cache(self, layer: int):
+        """One layer's cache: ``[n_blocks, block_size, 2, n_kv_heads, head_dim]``, or the ``(keys, values)`` pair of a
+        cache described by ``layer_shapes``."""
+        if self._split is not None:
+            return self._split[layer]
         return self._cache[layer]
 
     # ----------------------------------------------------------------------- host offload of blocks
@@ -69,6 +88,8 @@ class BlockedKVCache:
         the caller keeps it and hands it back to :meth:`restore`.  (The reference declares both methods and raises
         ``NotImplementedError``, ``kv_cache.py:166-184``.)"""
         ids = torch.as_tensor(blocks, dtype=torch.long).reshape(-1)
+        if self._split is not None:
+            raise NotImplementedError("host offload of a cache with per-layer shapes")
         picked = self._cache.index_select(1, ids.to(self._cache.device))
         if self._cache.is_cuda:
             host = torch.empty(picked.shape, dtype=picked.dtype, device="cpu", pin_memory=True)
@@ -90,7 +111,7 @@ class BlockedKVCache:
 
     @property
     def num_caches(self) -> int:
-        return self._cache.shape[0]
+        return len(self._split) if self._split is not None else self._cache.shape[0]
 
     @property
     def free_blocks(self) -> int:

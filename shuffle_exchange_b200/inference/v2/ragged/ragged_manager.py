@@ -32,8 +32,15 @@ class DSStateManagerConfig:
 
 
 class DSStateManager:
-    def __init__(self, config: DSStateManagerConfig, kv_config: KVCacheConfig, device=None, mp_group=None) -> None:
+    def __init__(self, config: DSStateManagerConfig, kv_config: KVCacheConfig, device=None, mp_group=None,
+                 state_config=None) -> None:
+        """``state_config``: a :class:`~.state_pool.StatePoolConfig` for models with recurrent layers; every tracked
+        sequence then owns one slot of the pool from its first forward until it is flushed."""
         self._config, self._kv_config = config, kv_config
+        self._state_pool = None
+        if state_config is not None and state_config.entries:
+            from .state_pool import RecurrentStatePool
+            self._state_pool = RecurrentStatePool(state_config, config.max_tracked_sequences, device=device)
         self._seqs: Dict[int, DSSequenceDescriptor] = {}
         num_blocks, reserve = config.num_kv_blocks, None
         mc = config.memory_config
@@ -56,6 +63,8 @@ class DSStateManager:
             if len(self._seqs) >= self._config.max_tracked_sequences:
                 raise RuntimeError(f"Unable to create tracking slot for sequence {uid}: too many tracked sequences")
             seq = self._seqs[uid] = DSSequenceDescriptor(uid, self.max_blocks_per_seq)
+            if self._state_pool is not None:
+                seq.state_slot = self._state_pool.acquire()
         return seq
 
     def flush_sequence(self, uid: int) -> None:
@@ -64,6 +73,9 @@ class DSStateManager:
             return
         if not seq.is_offloaded:
             self._kv_cache.free(seq.kv_blocks())
+        if self._state_pool is not None and seq.state_slot >= 0:
+            self._state_pool.release(seq.state_slot)
+            seq.state_slot = -1
 
     # ------------------------------------------------------------------ suspending sequences to host
     def offload_sequence(self, uid: int) -> int:
@@ -98,6 +110,14 @@ class DSStateManager:
 
     def get_cache(self, layer: int) -> torch.Tensor:
         return self._kv_cache.get_cache(layer)
+
+    def get_state(self, entry: int) -> torch.Tensor:
+        """Tensor ``[slots, *shape]`` of one entry of the recurrent-state pool."""
+        return self._state_pool.get(entry)
+
+    @property
+    def free_state_slots(self) -> int:
+        return self._state_pool.free_slots if self._state_pool is not None else self._config.max_tracked_sequences
 
     @property
     def free_blocks(self) -> int:

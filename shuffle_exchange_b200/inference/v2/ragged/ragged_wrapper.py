@@ -1,7 +1,8 @@
 """Host-side assembly of one ragged batch and its upload (reference: ``inference/v2/ragged/ragged_wrapper.py:31-292``).
 
 All metadata of a forward pass lives in ONE pinned int32 staging buffer laid out as
-``[token ids | token->sequence | token position | last-token index per sequence | block tables | attention atoms]`` and
+``[token ids | token->sequence | token position | rows whose logits are wanted | block tables | attention atoms |
+per-sequence info]`` and
 is uploaded with a single ``cudaMemcpyAsync`` in ``finalize`` (the reference uses three pinned "fast host buffers",
 ``ragged/csrc/fast_host_buffer.cu``).  The attention atoms (one per 128-query tile of a sequence, with the KV extent
 it attends to) are cut by the native scheduler ``sxbh_build_atoms`` (``csrc/host/ragged_host.cpp``) at ``finalize``
@@ -20,7 +21,7 @@ class RaggedBatchWrapper:
         self.max_tokens, self.max_seqs, self.max_blocks = max_ragged_batch_size, max_ragged_sequence_count, max_blocks_per_seq
         self.device = device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu")
         self.max_atoms = self.max_tokens // ATOM_Q_BLOCK + self.max_seqs
-        n = 3 * self.max_tokens + self.max_seqs + self.max_seqs * self.max_blocks + 6 * self.max_atoms
+        n = 4 * self.max_tokens + self.max_seqs * self.max_blocks + 6 * self.max_atoms + 4 * self.max_seqs
         self._seq_meta = torch.zeros(3, self.max_seqs, dtype=torch.int32)      # start / in-flight tokens / seen tokens
         pin = torch.cuda.is_available()
         self._host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
@@ -31,29 +32,40 @@ class RaggedBatchWrapper:
         self._n_tokens = 0
         self._n_seqs = 0
         self._n_atoms = 0
+        self._n_logit_rows = 0
         self._finalized = False
 
     def _views(self, buf):
         T, S, B = self.max_tokens, self.max_seqs, self.max_blocks
-        e = 3 * T + S + S * B
-        return (buf[0:T], buf[T:2 * T], buf[2 * T:3 * T], buf[3 * T:3 * T + S], buf[3 * T + S:e].view(S, B),
-                buf[e:].view(self.max_atoms, 6))
+        e = 4 * T + S * B
+        f = e + 6 * self.max_atoms
+        return (buf[0:T], buf[T:2 * T], buf[2 * T:3 * T], buf[3 * T:4 * T], buf[4 * T:e].view(S, B),
+                buf[e:f].view(self.max_atoms, 6), buf[f:].view(S, 4))
 
-    def insert_sequence(self, seq_descriptor, tokens: torch.Tensor, do_checks: bool = True) -> None:
+    def insert_sequence(self, seq_descriptor, tokens: torch.Tensor, do_checks: bool = True, logit_rows=None) -> None:
+        """``logit_rows``: indices among ``tokens`` whose logits the forward returns (default: the last token)."""
         n = tokens.numel()
         if do_checks:
             if self._n_tokens + n > self.max_tokens:
                 raise RuntimeError(f"Ragged batch is full due to tokens: {self._n_tokens} + {n} > {self.max_tokens}")
             if self._n_seqs + 1 > self.max_seqs:
                 raise RuntimeError("Ragged batch is full due to sequences")
-        ids, t2s, pos, last, tables, _ = self._views(self._host)
+        ids, t2s, pos, last, tables, _, info = self._views(self._host)
         a, b = self._n_tokens, self._n_tokens + n
         self._seq_meta[0, self._n_seqs], self._seq_meta[1, self._n_seqs] = a, n
         self._seq_meta[2, self._n_seqs] = seq_descriptor.seen_tokens
         ids[a:b] = tokens.to(torch.int32)
         t2s[a:b] = self._n_seqs
         pos[a:b] = torch.arange(seq_descriptor.seen_tokens, seq_descriptor.seen_tokens + n, dtype=torch.int32)
-        last[self._n_seqs] = b - 1
+        rows = [n - 1] if logit_rows is None else [int(r) for r in logit_rows]
+        if any(r < 0 or r >= n for r in rows):
+            raise ValueError(f"logit rows {rows} outside the {n} tokens of the sequence")
+        for r in rows:
+            last[self._n_logit_rows] = a + r
+            self._n_logit_rows += 1
+        info[self._n_seqs, 0], info[self._n_seqs, 1] = a, n
+        info[self._n_seqs, 2] = seq_descriptor.seen_tokens
+        info[self._n_seqs, 3] = getattr(seq_descriptor, "state_slot", -1)
         blocks = seq_descriptor.kv_blocks()
         tables[self._n_seqs, : blocks.numel()] = blocks
         self._n_tokens, self._n_seqs = b, self._n_seqs + 1
@@ -83,7 +95,15 @@ class RaggedBatchWrapper:
         return self._views(self._dev)[2][: self._n_tokens]
 
     def last_token_index(self):
-        return self._views(self._dev)[3][: self._n_seqs]
+        """Batch rows whose logits are returned: every sequence's last token unless ``insert_sequence`` named others."""
+        return self._views(self._dev)[3][: self._n_logit_rows]
+
+    def seq_info(self):
+        """int32 ``[n_seqs, 4]`` on the device: (first row, rows, tokens seen before this forward, state slot or -1)."""
+        return self._views(self._dev)[6][: self._n_seqs]
+
+    def host_seq_info(self):
+        return self._views(self._host)[6][: self._n_seqs]
 
     def block_tables(self):
         return self._views(self._dev)[4]

@@ -47,6 +47,7 @@ class DSSequenceDescriptor(BaseSequenceDescriptor):
         self._blocks = torch.zeros(max_blocks, dtype=torch.int32)
         self._n_blocks = 0
         self._host_kv = None          # host copy of the KV blocks while the sequence is offloaded
+        self.state_slot = -1          # slot of the recurrent-state pool (models with recurrent layers), else -1
 
     @property
     def tracking_id(self) -> int:
