@@ -22,6 +22,30 @@ def build_engine_from_model(causal_lm, engine_config: RaggedInferenceEngineConfi
                              engine_config, device=device)
 
 
+def build_engine_from_state_dict(model_config: dict, state_dict, engine_config: RaggedInferenceEngineConfig = None,
+                                 dtype: torch.dtype = None, device=None) -> InferenceEngineV2:
+    """Engine for an architecture described by a plain ``config.json`` object (``{"architecture": name, ...}``) and a
+    ``{checkpoint name: tensor}`` mapping held in memory."""
+    from .checkpoint.base_engine import CheckpointEngineBase
+    from .checkpoint.huggingface_engine import PlainModelConfig
+
+    class _Tensors(CheckpointEngineBase):
+        def __init__(self):
+            super().__init__()
+            self.model_config = PlainModelConfig(dict(model_config))
+
+        def parameters(self):
+            return iter(state_dict.items())
+
+    engine_config = engine_config or RaggedInferenceEngineConfig()
+    ce = _Tensors()
+    policy = _policy_for(ce.model_config, ce)
+    policy._engine_config = engine_config
+    if dtype is not None:
+        policy.dtype_override = dtype
+    return InferenceEngineV2(policy, engine_config, device=device)
+
+
 def _policy_for(model_config, checkpoint_engine):
     mt = getattr(model_config, "model_type", "").lower()
     if mt not in POLICIES:

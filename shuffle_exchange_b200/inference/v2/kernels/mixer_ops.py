@@ -102,7 +102,7 @@ def qk_norm_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], kcache: torc
                   kcache.data_ptr(), vcache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), tables.data_ptr(), T,
                   tables.shape[1], bs, Hq, G, d, dv, float(eps), int(normalize), _dt(qkv), _lib.stream_ptr())
         return q
-    x = qkv.float() + (bias.float() if bias is not None else 0.0)
+    x = qkv[:, : (Hq + G) * d + G * dv].float() + (bias.float() if bias is not None else 0.0)
     q = x[:, : Hq * d].reshape(T, Hq, d)
     k = x[:, Hq * d: (Hq + G) * d].reshape(T, G, d)
     v = x[:, (Hq + G) * d:].reshape(T, G, dv)
