@@ -53,6 +53,13 @@ def parse():
     ap.add_argument("--ep-capacity-factor", type=float, default=2.0,
                     help="Mixtral fused exchange: receive-buffer rows per rank as a multiple of the balanced share (a "
                          "random-init router is unbalanced: 1.25 overflowed at 8 GPUs; overflow raises, nothing is dropped)")
+    ap.add_argument("--serve", default="",
+                    help="instead of the training step: serving throughput (prefill and decode through the ragged "
+                         "engine) of the hybrid Fomalix stack beside a Llama stack of equal size, for the comma-separated "
+                         "sizes (w1024, w2048, w4096; 'all'), with device times of their kernels against the memory roofline")
+    ap.add_argument("--serve-prefill", type=int, default=4096)
+    ap.add_argument("--serve-batch", type=int, default=64)
+    ap.add_argument("--serve-context", type=int, default=2560)
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary measurements (exposed communication, fused-path rooflines, the line at "
                          "the reference's recompute setting)")
@@ -461,6 +468,12 @@ def main():
     args = parse()
     if args.moe_fused:
         args.moe_nccl = False
+    if args.serve:
+        from shuffle_exchange_b200.inference.v2 import serve_bench
+        sizes = list(serve_bench.SIZES) if args.serve == "all" else args.serve.split(",")
+        print(json.dumps(serve_bench.run(sizes, args.serve_prefill, args.serve_batch, args.serve_context, args.steps,
+                                         args.warmup)))
+        return
     if args.impl == "reference":
         try:
             run_reference(args)

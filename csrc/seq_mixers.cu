@@ -16,6 +16,7 @@
 //   group_norm_gate       RMS norm over channel groups combined with a SiLU gate (before or after the norm)
 //   gated_act_rows        act(gate) * up for any width and fp32 or bf16 rows
 #include "sxb_common.cuh"
+#include <cuda_pipeline.h>
 
 namespace sxb {
 namespace seqmix {
@@ -132,6 +133,168 @@ qk_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restri
 }
 
 constexpr int kMaxVPerLane = 8;      // value head size <= 256
+constexpr int kShortAtom = 16;       // atoms of at most this many queries run one warp per (query, head)
+constexpr int kBQ = 64, kBK = 64;    // query rows / keys per tile of the tiled kernel
+
+template <typename T>
+__device__ __forceinline__ float4 load4_f32(const T* p);
+template <>
+__device__ __forceinline__ float4 load4_f32<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4_f32<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+// Tiled form for atoms of many queries (prompt portions): one CTA per (64 queries of an atom, query head).  Q (scaled),
+// one 64-key tile of K and V (converted to fp32) and the tile's weights sit in shared memory; 256 threads hold 4x4
+// scores and 4 x (dv/16) outputs each.  Scores, online softmax with the sink logit, and the weighted sum are fp32 FMAs:
+// the weights must stay 32-bit, so the products cannot go through the bf16 tensor path.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
+                           const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ atoms,
+                           const int* __restrict__ tables, int max_blocks, int block_size, int Hq, int G, int d,
+                           int dv, float scale, int chunk) {
+  extern __shared__ __align__(16) float smf[];
+  const int dp = d + 4, vp = NV * 64, pp = kBK + 4;
+  float* Qs = smf;
+  float* Ks = Qs + kBQ * dp;
+  float* Vs = Ks + kBK * dp;
+  float* Ps = Vs + kBK * vp;
+  const int* a = atoms + 6 * (blockIdx.x >> 1);
+  const int sub = blockIdx.x & 1;
+  const int nq = min(a[2] - sub * kBQ, kBQ);
+  if (nq <= 0) return;
+  const int row0 = a[1] + sub * kBQ, pos0 = a[3] + sub * kBQ;
+  const int h = blockIdx.y, g = h / (Hq / G);
+  const int* tab = tables + (long long)a[0] * max_blocks;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int d4 = d >> 2;
+  for (int i = tid; i < kBQ * d4; i += 256) {
+    const int r = i / d4, c = (i % d4) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nq) v = *reinterpret_cast<const float4*>(q + ((long long)(row0 + r) * Hq + h) * d + c);
+    v.x *= scale, v.y *= scale, v.z *= scale, v.w *= scale;
+    *reinterpret_cast<float4*>(Qs + r * dp + c) = v;
+  }
+  float m[4], l[4], acc[4][NV * 4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m[i] = sink ? sink[h] : -INFINITY;
+    l[i] = sink ? 1.f : 0.f;
+#pragma unroll
+    for (int c = 0; c < NV * 4; ++c) acc[i][c] = 0.f;
+  }
+  const int last = pos0 + nq - 1;
+  const int kbeg = chunk > 0 ? (pos0 / chunk) * chunk : 0;
+  for (int k0 = kbeg; k0 <= last; k0 += kBK) {
+    __syncthreads();
+    for (int i = tid; i < kBK * d4; i += 256) {
+      const int r = i / d4, c = (i % d4) * 4, kj = k0 + r;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kj <= last) {
+        const long long slot = (long long)tab[kj / block_size] * block_size + kj % block_size;
+        v = load4_f32<T>(kcache + (slot * G + g) * d + c);
+      }
+      *reinterpret_cast<float4*>(Ks + r * dp + c) = v;
+    }
+    for (int i = tid; i < kBK * (vp >> 2); i += 256) {
+      const int r = i / (vp >> 2), c = (i % (vp >> 2)) * 4, kj = k0 + r;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kj <= last && c < dv) {
+        const long long slot = (long long)tab[kj / block_size] * block_size + kj % block_size;
+        v = load4_f32<T>(vcache + (slot * G + g) * dv + c);
+      }
+      *reinterpret_cast<float4*>(Vs + r * vp + c) = v;
+    }
+    __syncthreads();
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    for (int c = 0; c < d; c += 4) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * dp + c);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * dp + c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          s[i][j] += qv[i].x * kv[j].x + qv[i].y * kv[j].y + qv[i].z * kv[j].z + qv[i].w * kv[j].w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty + 16 * i, qp = pos0 + r;
+      const int lo = chunk > 0 ? (qp / chunk) * chunk : 0;
+      float mt = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kj = k0 + tx + 16 * j;
+        if (!(r < nq && kj <= qp && kj >= lo)) s[i][j] = -INFINITY;
+        mt = fmaxf(mt, s[i][j]);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+      const float mn = fmaxf(m[i], mt);
+      const float corr = (mn == -INFINITY) ? 1.f : expf(m[i] - mn);
+      float ps = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float p = (s[i][j] == -INFINITY) ? 0.f : expf(s[i][j] - mn);
+        ps += p;
+        Ps[r * pp + tx + 16 * j] = p;
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      l[i] = l[i] * corr + ps;
+      m[i] = mn;
+#pragma unroll
+      for (int c = 0; c < NV * 4; ++c) acc[i][c] *= corr;
+    }
+    __syncwarp();          // a row of weights is written and read by the 16 threads of one half-warp
+    for (int j = 0; j < kBK; j += 4) {
+      float4 pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * pp + j);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+          const float4 vv = *reinterpret_cast<const float4*>(Vs + (j + jj) * vp + n * 64 + tx * 4);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float p = jj == 0 ? pv[i].x : (jj == 1 ? pv[i].y : (jj == 2 ? pv[i].z : pv[i].w));
+            acc[i][n * 4 + 0] += p * vv.x;
+            acc[i][n * 4 + 1] += p * vv.y;
+            acc[i][n * 4 + 2] += p * vv.z;
+            acc[i][n * 4 + 3] += p * vv.w;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty + 16 * i;
+    if (r >= nq) continue;
+    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+#pragma unroll
+    for (int n = 0; n < NV; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int c = n * 64 + tx * 4 + e;
+        if (c < dv) out[((long long)(row0 + r) * Hq + h) * dv + c] = from_f32<T>(acc[i][n * 4 + e] * inv);
+      }
+  }
+}
 
 // One warp per (token, query head).  Keys lo..pos of the token's sequence, lo = start of the token's chunk
 // (chunk > 0) or 0.  The softmax denominator starts from exp(sink[h]): a logit without a key or a value.
@@ -140,17 +303,25 @@ __global__ void __launch_bounds__(128)
 sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                       const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
                       const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
-                      int Hq, int G, int d, int dv, float scale, int chunk) {
+                      int Hq, int G, int d, int dv, float scale, int chunk, const int* __restrict__ atoms) {
   extern __shared__ float qs[];      // [warps][d]
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int h = blockIdx.y * nw + warp;
   if (h >= Hq) return;
+  int t = blockIdx.x, pos, seq;
+  if (atoms != nullptr) {            // tokens of short atoms: kShortAtom grid slots per atom
+    const int* a = atoms + 6 * (blockIdx.x / kShortAtom);
+    const int i = blockIdx.x % kShortAtom;
+    if (i >= a[2]) return;
+    t = a[1] + i, pos = a[3] + i, seq = a[0];
+  } else {
+    pos = tok_pos[t], seq = tok_seq[t];
+  }
   float* myq = qs + warp * d;
   for (int c = lane; c < d; c += 32) myq[c] = q[((long long)t * Hq + h) * d + c];
   __syncwarp();
   const int g = h / (Hq / G);
-  const int pos = tok_pos[t];
-  const int* tab = tables + (long long)tok_seq[t] * max_blocks;
+  const int* tab = tables + (long long)seq * max_blocks;
   const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
   float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   float acc[kMaxVPerLane];
@@ -285,12 +456,10 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
                          const float* __restrict__ beta, const float* __restrict__ skip, float* __restrict__ state,
                          float* __restrict__ out, const int* __restrict__ seq_info, int H, int G, int n, int dv,
                          int delta) {
-  extern __shared__ float sm[];          // k [TB][n] | q [TB][n] | v [TB][kCols] | decay [TB] | beta [TB]
-  float* sk = sm;
-  float* sq = sk + kTB * n;
-  float* sv = sq + kTB * n;
-  float* sa = sv + kTB * kCols;
-  float* sb = sa + kTB;
+  // two staging buffers, each k [TB][n] | q [TB][n] | v [TB][kCols] | decay [TB] | beta [TB]: the next TB tokens are
+  // copied in (cp.async) while the current ones are walked
+  extern __shared__ float sm[];
+  const int stage = 2 * kTB * n + kTB * kCols + 2 * kTB;
   const int* si = seq_info + 4 * blockIdx.z;
   const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
   const int h = blockIdx.y, g = h / (H / G);
@@ -305,36 +474,61 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     S[r] = (live && seen > 0 && i < n) ? sp[i] : 0.f;
   }
   const float D = skip ? skip[h] : 0.f;
-  for (int t0 = 0; t0 < rows; t0 += kTB) {
+
+  auto stage_in = [&](int buf, int t0) {
+    float* sk = sm + buf * stage;
+    float* sq = sk + kTB * n;
+    float* sv = sq + kTB * n;
+    float* sa = sv + kTB * kCols;
+    float* sb = sa + kTB;
     const int nt = min(kTB, rows - t0);
-    __syncthreads();
     for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
       const long long row = first + t0 + i / n;
-      sk[i] = kvec[row * ldkq + g * n + i % n];
-      sq[i] = qvec[row * ldkq + g * n + i % n];
+      __pipeline_memcpy_async(sk + i, kvec + row * ldkq + g * n + i % n, 4);
+      __pipeline_memcpy_async(sq + i, qvec + row * ldkq + g * n + i % n, 4);
     }
     for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
-      const int c = blockIdx.x * kCols + i % kCols;
-      sv[i] = c < dv ? val[(long long)(first + t0 + i / kCols) * ldv + h * dv + c] : 0.f;
+      const int c = min(blockIdx.x * kCols + i % kCols, dv - 1);
+      __pipeline_memcpy_async(sv + i, val + (long long)(first + t0 + i / kCols) * ldv + h * dv + c, 4);
     }
     for (int i = threadIdx.x; i < nt; i += blockDim.x) {
-      sa[i] = decay[(long long)(first + t0 + i) * H + h];
-      sb[i] = beta[(long long)(first + t0 + i) * H + h];
+      __pipeline_memcpy_async(sa + i, decay + (long long)(first + t0 + i) * H + h, 4);
+      __pipeline_memcpy_async(sb + i, beta + (long long)(first + t0 + i) * H + h, 4);
     }
+    __pipeline_commit();
+  };
+
+  stage_in(0, 0);
+  int buf = 0;
+  for (int t0 = 0; t0 < rows; t0 += kTB, buf ^= 1) {
+    const int nt = min(kTB, rows - t0);
+    const bool more = t0 + kTB < rows;
+    if (more) stage_in(buf ^ 1, t0 + kTB);
+    if (more) __pipeline_wait_prior(1);
+    else __pipeline_wait_prior(0);
     __syncthreads();
+    const float* sk = sm + buf * stage;
+    const float* sq = sk + kTB * n;
+    const float* sv = sq + kTB * n;
+    const float* sa = sv + kTB * kCols;
+    const float* sb = sa + kTB;
     for (int tt = 0; tt < nt; ++tt) {
       const float a = sa[tt], b = sb[tt], v = sv[tt * kCols + lc];
       const float* kk = sk + tt * n;
       const float* qq = sq + tt * n;
       float u = b * v;
       if (delta) {
-        float dot = 0.f;
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
+        for (int r = 0; r < R; r += 4) {
+          S[r] *= a, S[r + 1] *= a, S[r + 2] *= a, S[r + 3] *= a;
           const int i = l + kLPC * r;
-          S[r] *= a;
-          if (i < n) dot += S[r] * kk[i];
+          if (i < n) d0 += S[r] * kk[i];
+          if (i + kLPC < n) d1 += S[r + 1] * kk[i + kLPC];
+          if (i + 2 * kLPC < n) d2 += S[r + 2] * kk[i + 2 * kLPC];
+          if (i + 3 * kLPC < n) d3 += S[r + 3] * kk[i + 3 * kLPC];
         }
+        float dot = (d0 + d1) + (d2 + d3);
         dot += __shfl_xor_sync(0xffffffffu, dot, 1);
         dot += __shfl_xor_sync(0xffffffffu, dot, 2);
         dot += __shfl_xor_sync(0xffffffffu, dot, 4);
@@ -343,20 +537,22 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
 #pragma unroll
         for (int r = 0; r < R; ++r) S[r] *= a;
       }
-      float o = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
+      for (int r = 0; r < R; r += 4) {
         const int i = l + kLPC * r;
-        if (i < n) {
-          S[r] += kk[i] * u;
-          o += S[r] * qq[i];
-        }
+        if (i < n) S[r] += kk[i] * u, o0 += S[r] * qq[i];
+        if (i + kLPC < n) S[r + 1] += kk[i + kLPC] * u, o1 += S[r + 1] * qq[i + kLPC];
+        if (i + 2 * kLPC < n) S[r + 2] += kk[i + 2 * kLPC] * u, o2 += S[r + 2] * qq[i + 2 * kLPC];
+        if (i + 3 * kLPC < n) S[r + 3] += kk[i + 3 * kLPC] * u, o3 += S[r + 3] * qq[i + 3 * kLPC];
       }
+      float o = (o0 + o1) + (o2 + o3);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       o += __shfl_xor_sync(0xffffffffu, o, 4);
       if (live && l == 0) out[(long long)(first + t0 + tt) * H * dv + h * dv + col] = o + D * v;
     }
+    __syncthreads();          // the buffer just walked is the target of the next iteration's copies
   }
   if (live) {
 #pragma unroll
@@ -465,7 +661,7 @@ SXB_API int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, 
 
 /* Attention of every token over the cached keys lo..pos of its sequence (lo = start of its chunk of `chunk` positions,
  * or 0 when chunk == 0), scores and weights in fp32; sink (fp32 [Hq] or null) adds exp(sink[h]) to the denominator.
- * out `dtype` [n_tokens, Hq * dv]. */
+ * out `dtype` [n_tokens, Hq * dv].  One warp per (token, head). */
 SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
                                int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
@@ -477,8 +673,58 @@ SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vc
   SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, warps * 32, warps * d * sizeof(float), (cudaStream_t)stream>>>(
                              (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out,
                              (const int*)tok_seq, (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq,
-                             G, d, dv, scale, chunk)));
+                             G, d, dv, scale, chunk, nullptr)));
   SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+template <typename T, int NV>
+static int launch_attention_tiles(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
+                                  const void* atoms, int n_long, const void* tables, int max_blocks, int block_size,
+                                  int Hq, int G, int d, int dv, float scale, int chunk, cudaStream_t s) {
+  const size_t smem = (size_t)(2 * kBQ * (d + 4) + kBK * NV * 64 + kBQ * (kBK + 4)) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(sink_attention_tile_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  sink_attention_tile_kernel<T, NV><<<dim3(2 * n_long, Hq), 256, smem, s>>>(
+      (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)atoms,
+      (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk);
+  return SXB_OK;
+}
+
+/* The same attention scheduled by attention atoms int32 [n_atoms, 6] = (sequence, first row, queries, first position,
+ * -, -), longest first: the first n_long atoms (more than 16 queries, at most 128) run the tiled kernel, 64 queries per
+ * CTA; the others one warp per (query, head).  Needs d and dv multiples of 4 and at most 256. */
+SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
+                                     const void* atoms, int n_atoms, int n_long, const void* tables, int max_blocks,
+                                     int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int dtype,
+                                     void* stream) {
+  if (n_atoms <= 0) return SXB_OK;
+  if (d % 4 || dv % 4 || d > 256 || dv > 256 || Hq % G || n_long < 0 || n_long > n_atoms) return SXB_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n_long > 0) {
+    const int nv = (dv + 63) / 64;
+    int rc = SXB_OK;
+#define TILES(NV)                                                                                                     \
+  SEQMIX_DISPATCH(dtype, (rc = launch_attention_tiles<T, NV>(q, kcache, vcache, sink, out, atoms, n_long, tables,      \
+                                                              max_blocks, block_size, Hq, G, d, dv, scale, chunk, s)))
+    if (nv == 1) TILES(1);
+    else if (nv == 2) TILES(2);
+    else if (nv == 3) TILES(3);
+    else TILES(4);
+#undef TILES
+    if (rc != SXB_OK) return rc;
+    SXB_CHECK_LAUNCH();
+  }
+  if (n_atoms > n_long) {
+    const int warps = 4;
+    dim3 grid((n_atoms - n_long) * kShortAtom, (Hq + warps - 1) / warps);
+    const int* rest = (const int*)atoms + 6 * n_long;
+    SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, warps * 32, warps * d * sizeof(float), s>>>(
+                               (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, nullptr,
+                               nullptr, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, rest)));
+    SXB_CHECK_LAUNCH();
+  }
   return SXB_OK;
 }
 
@@ -547,7 +793,7 @@ SXB_API int sxb_linear_recurrence(const void* kvec, const void* qvec, long long 
   if (n_seqs <= 0) return SXB_OK;
   if (n > 256 || H % G) return SXB_ERR_UNSUPPORTED;
   dim3 grid((dv + kCols - 1) / kCols, H, n_seqs);
-  const size_t smem = (size_t)(2 * kTB * n + kTB * kCols + 2 * kTB) * sizeof(float);
+  const size_t smem = (size_t)2 * (2 * kTB * n + kTB * kCols + 2 * kTB) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
 #define LAUNCH_REC(R)                                                                                              \
   linear_recurrence_kernel<R><<<grid, kLPC * kCols, smem, s>>>(                                                     \

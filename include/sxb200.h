@@ -476,6 +476,12 @@ int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, const vo
                         int n_tokens, int C, int gs, float eps, int gate_first, int dtype, void* stream);
 int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, void* stream);
 
+/* ---- csrc/seq_mixers.cu */
+int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
+                             const void* atoms, int n_atoms, int n_long, const void* tables, int max_blocks,
+                             int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int dtype,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,6 +21,7 @@ _lib.register({
     "sxb_resid_norm_step": "pppppp" "l" "i" "f" "i" "p",
     "sxb_qk_norm_append": "p" "l" "ppppppp" "iiiiiii" "f" "ii" "p",
     "sxb_sink_attention": "pppppppp" "iiiiiii" "f" "ii" "p",
+    "sxb_sink_attention_atoms": "pppppp" "ii" "p" "iiiiii" "f" "ii" "p",
     "sxb_conv_silu": "p" "l" "pppppp" "iii" "i" "p",
     "sxb_conv_state_update": "p" "l" "pp" "iii" "i" "p",
     "sxb_unit_norm_heads": "p" "l" "iii" "ff" "i" "p",
@@ -115,16 +116,32 @@ def qk_norm_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], kcache: torc
     return q.contiguous()
 
 
+SHORT_ATOM = 16          # atoms of at most this many queries run one warp per (query, head)
+
+
+def tiles_supported(d: int, dv: int) -> bool:
+    return d % 4 == 0 and dv % 4 == 0 and d <= 256 and dv <= 256
+
+
 def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, sink: Optional[torch.Tensor],
                    tok_seq: torch.Tensor, tok_pos: torch.Tensor, tables: torch.Tensor, scale: float, chunk: int,
-                   out_dtype: torch.dtype) -> torch.Tensor:
+                   out_dtype: torch.dtype, atoms: Optional[torch.Tensor] = None, n_long: int = 0) -> torch.Tensor:
     """Softmax attention of each token (fp32 ``q`` ``[T, Hq, d]``) over the cached keys ``lo..pos`` of its sequence,
     ``lo`` = first position of the token's chunk of ``chunk`` positions (0: plain causal).  ``sink`` (fp32 ``[Hq]``)
-    adds ``exp(sink[h])`` to the denominator.  Returns ``[T, Hq * dv]``."""
+    adds ``exp(sink[h])`` to the denominator.  Returns ``[T, Hq * dv]``.
+
+    With the batch's attention ``atoms`` (longest first) of which the first ``n_long`` hold more than
+    :data:`SHORT_ATOM` queries, those run the tiled kernel (64 queries per CTA, K/V tiles shared by them) and the rest
+    one warp per (query, head); without atoms every token takes the latter."""
     T, Hq, d = q.shape
     bs, G, dv = kcache.shape[1], kcache.shape[2], vcache.shape[3]
     if q.is_cuda:
         out = torch.empty(T, Hq * dv, dtype=out_dtype, device=q.device)
+        if atoms is not None and n_long > 0 and tiles_supported(d, dv):
+            _lib.call("sxb_sink_attention_atoms", q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), _lib.ptr(sink),
+                      out.data_ptr(), atoms.data_ptr(), atoms.shape[0], int(n_long), tables.data_ptr(), tables.shape[1],
+                      bs, Hq, G, d, dv, float(scale), int(chunk), _lib.dtype_code(out_dtype), _lib.stream_ptr())
+            return out
         _lib.call("sxb_sink_attention", q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), _lib.ptr(sink),
                   out.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), tables.data_ptr(), T, tables.shape[1], bs, Hq,
                   G, d, dv, float(scale), int(chunk), _lib.dtype_code(out_dtype), _lib.stream_ptr())

@@ -389,8 +389,11 @@ class DSSinkChunkedAttention(DSSelfAttentionBase):
         t2s, pos, tables = batch.token_to_seq(), batch.token_positions(), batch.block_tables()
         q = M.qk_norm_append(q_k_v, bias, keys, values, t2s, pos, tables, c.n_heads_q, c.n_heads_kv, c.head_size, dv,
                              c.qk_norm_eps, c.qk_unit_rms)
+        atoms, n_long = None, 0
+        if q.is_cuda and M.tiles_supported(c.head_size, dv) and hasattr(batch, "atoms_longer_than"):
+            atoms, n_long = batch.atoms(), batch.atoms_longer_than(M.SHORT_ATOM)
         return M.sink_attention(q, keys, values, sink if c.sink else None, t2s, pos, tables, c.scale_factor, chunk,
-                                _dt(c.output_dtype).torch)
+                                _dt(c.output_dtype).torch, atoms, n_long)
 
 
 @DSEmbeddingRegistry.register_module

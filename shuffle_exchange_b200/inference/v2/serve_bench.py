@@ -1,0 +1,269 @@
+"""Serving throughput of a hybrid (Fomalix) stack next to a Llama stack of equal width, depth and feed-forward size, both
+through ``InferenceEngineV2.put`` with random weights, plus device times of the hybrid stack's kernels and of their Llama
+counterparts against the memory roofline.  ``bench.py --serve`` prints the result as one JSON object.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up forwards, a buffer larger than L2 is rewritten between timed
+forwards.  Prefill: one request of ``prefill`` tokens in one forward.  Decode: ``batch`` requests with ``context`` tokens
+each advance one token per forward.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Callable, Dict, List
+
+import torch
+
+from .config_v2 import RaggedInferenceEngineConfig
+from .engine_factory import build_engine_from_model, build_engine_from_state_dict
+from .ragged.ragged_manager import DSStateManagerConfig
+
+SIZES = {
+    "w1024": dict(width=1024, layers=6, heads=8, kv_heads=2, head=128, ff=4096, ssd_heads=16, ssd_vdim=128, state=128),
+    "w2048": dict(width=2048, layers=6, heads=16, kv_heads=4, head=128, ff=8192, ssd_heads=32, ssd_vdim=128, state=128),
+    "w4096": dict(width=4096, layers=3, heads=32, kv_heads=8, head=128, ff=14336, ssd_heads=64, ssd_vdim=128, state=128),
+}
+VOCAB = 32000
+CHUNK = 1024
+
+
+def hybrid_config(z: Dict) -> Dict:
+    kinds = ["delta", "mamba2", "attention"]
+    mixers = {
+        "delta": {"conv": 4, "dim": z["head"], "heads": z["heads"], "kv_heads": z["heads"], "vdim": z["head"]},
+        "mamba2": {"conv": 4, "groups": 1, "heads": z["ssd_heads"], "norm_groups": 1, "state": z["state"],
+                   "vdim": z["ssd_vdim"]},
+        "attention": {"dim": z["head"], "heads": z["heads"], "kv_heads": z["kv_heads"], "mask": {"size": CHUNK},
+                      "scale": z["head"] ** -0.5, "vdim": z["head"]},
+    }
+    layers = [{"type": kinds[i % 3], "mixer": mixers[kinds[i % 3]], "mlp": {"ff": z["ff"], "kind": "dense"}}
+              for i in range(z["layers"])]
+    return {"architecture": "Fomalix", "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-5},
+            "vocab": VOCAB, "width": z["width"]}
+
+
+def hybrid_weights(cfg: Dict, device) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(0)
+    W = cfg["width"]
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g, device=device) / math.sqrt(i)).to(torch.bfloat16)
+
+    def vec(n, lo=0.5, hi=1.5, dt=torch.bfloat16):
+        return (torch.rand(n, generator=g, device=device) * (hi - lo) + lo).to(dt)
+
+    out = {"embed": mat(cfg["vocab"], W), "head": mat(cfg["vocab"], W), "final.norm": vec(W)}
+    for i, L in enumerate(cfg["layers"]):
+        m, p = L["mixer"], f"l{i}."
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            out[p + n] = vec(W)
+        ff = L["mlp"]["ff"]
+        out[p + "mlp.gate"], out[p + "mlp.up"], out[p + "mlp.down"] = mat(ff, W), mat(ff, W), mat(W, ff)
+        if L["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, o in (("q", H * d), ("k", G * d), ("v", G * dv)):
+                out[p + "mix." + n], out[p + "mix." + n + ".b"] = mat(o, W), vec(o, -0.1, 0.1)
+            out[p + "mix.sink"], out[p + "mix.o"] = vec(H, -1, 1), mat(W, H * dv)
+        elif L["type"] == "delta":
+            H, G, d, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for n, o in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                out[p + "mix." + n], out[p + "mix." + n + ".conv"] = mat(o, W), vec(o * taps, -0.5, 0.5).view(o, taps)
+            out[p + "mix.b"], out[p + "mix.a"] = mat(H, W), mat(H, W)
+            out[p + "mix.A_log"], out[p + "mix.dt_bias"] = vec(H, -2, 0.5), vec(H, -1, 1)
+            out[p + "mix.norm"], out[p + "mix.g"], out[p + "mix.o"] = vec(dv), mat(H * dv, W), mat(W, H * dv)
+        else:
+            H, dv, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            inner, ch = H * dv, H * dv + 2 * G * N
+            out[p + "mix.in"] = mat(2 * inner + 2 * G * N + H, W)
+            out[p + "mix.conv"], out[p + "mix.conv.b"] = vec(ch * taps, -0.5, 0.5).view(ch, taps), vec(ch, -0.1, 0.1)
+            out[p + "mix.dt_bias"], out[p + "mix.A_log"], out[p + "mix.D"] = vec(H, -1, 1), vec(H, -2, 0.5), vec(H)
+            out[p + "mix.norm"], out[p + "mix.o"] = vec(inner), mat(W, inner)
+    return out
+
+
+def _engine_config(max_tokens: int, max_seqs: int, pages: int) -> RaggedInferenceEngineConfig:
+    sm = DSStateManagerConfig(max_tracked_sequences=max_seqs, max_ragged_sequence_count=max_seqs,
+                              max_ragged_batch_size=max(max_tokens, max_seqs), max_context=8192, num_kv_blocks=pages)
+    return RaggedInferenceEngineConfig(state_manager=sm, kv_block_size=64)
+
+
+def build_hybrid(z: Dict, max_tokens: int, max_seqs: int, pages: int):
+    cfg = hybrid_config(z)
+    return build_engine_from_state_dict(cfg, hybrid_weights(cfg, "cuda"), _engine_config(max_tokens, max_seqs, pages),
+                                        dtype=torch.bfloat16)
+
+
+def build_llama(z: Dict, max_tokens: int, max_seqs: int, pages: int):
+    from ...models.llama import LlamaForCausalLM, llama_config
+    cfg = llama_config("llama-tiny", hidden_size=z["width"], num_hidden_layers=z["layers"],
+                       num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], intermediate_size=z["ff"],
+                       vocab_size=VOCAB, activation_checkpointing=False)
+    torch.manual_seed(0)
+    lm = LlamaForCausalLM(cfg, device="cuda", dtype=torch.bfloat16).eval()
+    return build_engine_from_model(lm, _engine_config(max_tokens, max_seqs, pages))
+
+
+class _Timer:
+    def __init__(self):
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")        # > 126 MB of L2
+
+    def __call__(self, fn: Callable[[], None], steps: int, warmup: int) -> float:
+        """Median device milliseconds of ``fn``."""
+        for _ in range(warmup):
+            fn()
+        times = []
+        for _ in range(steps):
+            self.flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        return sorted(times)[len(times) // 2]
+
+
+def engine_throughput(build, z: Dict, prefill: int, batch: int, context: int, steps: int, warmup: int, timer) -> Dict:
+    pages = (prefill + 63) // 64 + batch * ((context + steps + warmup + 8 + 63) // 64) + 8
+    eng = build(z, max(prefill, batch, 2048), batch + 1, pages)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, VOCAB, (prefill,), generator=g, dtype=torch.int32)
+    uid = [1000]
+
+    def one_prefill():
+        uid[0] += 1
+        eng.put([uid[0]], [prompt], do_checks=False)
+        eng.flush(uid[0])
+    ms_p = timer(one_prefill, steps, warmup)
+    uids = list(range(batch))
+    for lo in range(0, context, 2048):                       # build the contexts, 2048 tokens of one request at a time
+        n = min(2048, context - lo)
+        for u in uids:
+            eng.put([u], [torch.randint(0, VOCAB, (n,), generator=g, dtype=torch.int32)], do_checks=False)
+    toks = [torch.randint(0, VOCAB, (1,), generator=g, dtype=torch.int32) for _ in uids]
+    ms_d = timer(lambda: eng.put(uids, toks, do_checks=False), steps, warmup)
+    del eng
+    torch.cuda.empty_cache()
+    return {"prefill_tokens": prefill, "prefill_ms": round(ms_p, 3), "prefill_tok_s": round(prefill / ms_p * 1e3),
+            "decode_batch": batch, "decode_context": context, "decode_ms": round(ms_d, 3),
+            "decode_tok_s": round(batch / ms_d * 1e3)}
+
+
+def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs: float) -> List[Dict]:
+    """Device time, algorithmic bytes and fraction of the copy bandwidth for the hybrid stack's kernels and the Llama
+    kernels that do the like job, at prefill (one request) and decode (``batch`` requests) shapes."""
+    from ...ops import functional as F
+    from .kernels import mixer_ops as M
+    from .kernels import ragged_ops as R
+    from .ragged.ragged_wrapper import RaggedBatchWrapper
+    dev, bf = "cuda", torch.bfloat16
+    W, H, G, d = z["width"], z["heads"], z["kv_heads"], z["head"]
+    Hs, dvs, N = z["ssd_heads"], z["ssd_vdim"], z["state"]
+    rows: List[Dict] = []
+
+    def add(name, phase, fn, nbytes, flops=0.0):
+        ms = timer(fn, 5, 3)
+        rows.append({"kernel": name, "phase": phase, "ms": round(ms, 4), "GB_s": round(nbytes / ms / 1e6, 1),
+                     "of_measured_hbm": round(nbytes / ms / 1e6 / hbm_gbs, 3), "GFLOP_s": round(flops / ms / 1e6, 1)})
+
+    for phase, T, n_seq, seen in (("prefill", prefill, 1, 0), ("decode", batch, batch, context)):
+        per = T // n_seq
+        tot = seen + per
+        n_pages_seq = (tot + 63) // 64
+        t2s = torch.arange(n_seq, device=dev, dtype=torch.int32).repeat_interleave(per)
+        pos = (torch.arange(per, device=dev, dtype=torch.int32) + seen).repeat(n_seq)
+        tables = torch.arange(n_seq * n_pages_seq, device=dev, dtype=torch.int32).view(n_seq, n_pages_seq)
+        info = torch.tensor([[i * per, per, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        resid = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        w = torch.ones(W, device=dev, dtype=bf)
+        add("resid_norm_step (post-norm + add + pre-norm)", phase,
+            lambda: M.resid_norm_step(resid, y, w, None, w, 1e-5, bf), T * W * (4 + 4 + 2 + 2))
+        add("llama rms_norm with residual add", phase, lambda: F.rms_norm(y, w, 1e-5, y), T * W * 2 * 4)
+        # attention: append + attend
+        qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+        bias = torch.zeros((H + 2 * G) * d, device=dev, dtype=bf)
+        kc = torch.randn(n_seq * n_pages_seq, 64, G, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * n_pages_seq, 64, G, d, device=dev).to(bf)
+        sink = torch.zeros(H, device=dev)
+        add("qk_norm_append", phase,
+            lambda: M.qk_norm_append(qkv, bias, kc, vc, t2s, pos, tables, H, G, d, d, 1e-5, True),
+            T * ((H + 2 * G) * d * 2 + H * d * 4 + 2 * G * d * 2))
+        q32 = torch.randn(T, H, d, device=dev)
+        lo = (seen + per - 1) // CHUNK * CHUNK
+        keys_per_q = (min(per, CHUNK) + 1) / 2 if phase == "prefill" else (tot - lo)
+        kv_bytes = n_seq * (tot if phase == "prefill" else tot - lo) * 2 * G * d * 2
+        fl = 4.0 * T * H * d * keys_per_q
+        cache = torch.randn(n_seq * n_pages_seq, 64, 2, G, d, device=dev).to(bf)
+        add("llama kv_rotary_blocked", phase,
+            lambda: R.kv_rotary_blocked(qkv, cache, t2s, pos, tables, H, G, d, d, 10000.0),
+            T * ((H + 2 * G) * d * 2 * 2 + 2 * G * d * 2))
+        wrap = RaggedBatchWrapper(max(T, 64), n_seq, n_pages_seq, device=dev)
+
+        class _Seq:
+            def __init__(self, i):
+                self.seen_tokens, self._b = seen, tables[i].cpu()
+
+            def kv_blocks(self):
+                return self._b
+        for i in range(n_seq):
+            wrap.insert_sequence(_Seq(i), torch.zeros(per, dtype=torch.int32), do_checks=False)
+        wrap.finalize()
+        atoms, n_long = wrap.atoms(), wrap.atoms_longer_than(M.SHORT_ATOM)
+        add(f"sink_attention (chunk {CHUNK}, fp32 weights)", phase,
+            lambda: M.sink_attention(q32, kc, vc, sink, t2s, pos, tables, d ** -0.5, CHUNK, bf, atoms, n_long),
+            kv_bytes + T * H * d * 6, fl)
+        qv = qkv.view(T, H + 2 * G, d)[:, :H]
+        full_keys = (per + 1) / 2 if phase == "prefill" else tot
+        add("llama ragged_attention (full causal)", phase, lambda: R.ragged_attention(qv, cache, wrap),
+            n_seq * tot * 2 * G * d * 2 + T * H * d * 4, 4.0 * T * H * d * full_keys)
+        # recurrences
+        for name, Hh, Gg, n, dv, delta in (("delta", H, H, d, d, True), ("ssd", Hs, 1, N, dvs, False)):
+            C = (2 * Gg * n + Hh * dv)
+            x = torch.randn(T, C, device=dev).to(bf)
+            cw = torch.randn(C, 4, device=dev).to(bf)
+            cst = torch.zeros(n_seq, 3, C, device=dev, dtype=bf)
+            add(f"conv_silu + state update ({name} channels)", phase,
+                lambda: (M.conv_silu(x, cw, None, cst, info, t2s), M.conv_state_update(x, cst, info)),
+                T * C * (2 + 4) + n_seq * 3 * C * 4)
+            xc = torch.randn(T, C, device=dev)
+            xc[:, : 2 * Gg * n] /= math.sqrt(n)
+            decay, beta = torch.rand(T, Hh, device=dev) * 0.1 + 0.9, torch.rand(T, Hh, device=dev)
+            S = torch.zeros(n_seq, Hh, dv, n, device=dev)
+            state_bytes = n_seq * Hh * dv * n * 4 * (2 if seen else 1)
+            add(f"linear_recurrence ({name})", phase,
+                lambda: M.linear_recurrence(xc[:, : Gg * n], xc[:, Gg * n: 2 * Gg * n], xc[:, 2 * Gg * n:], decay, beta,
+                                            None, S, info, Hh, Gg, n, dv, delta),
+                state_bytes + T * (C * 4 + Hh * dv * 4), (6.0 if delta else 4.0) * T * Hh * dv * n)
+            o = torch.randn(T, Hh * dv, device=dev)
+            gate = torch.randn(T, Hh * dv, device=dev).to(bf)
+            nw = torch.ones(dv if delta else Hh * dv, device=dev, dtype=bf)
+            add(f"group_norm_gate ({name})", phase,
+                lambda: M.group_norm_gate(o, gate, nw, dv if delta else Hh * dv, 1e-5, not delta, bf),
+                T * Hh * dv * (4 + 2 + 2))
+    return rows
+
+
+def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, warmup: int, kernels: bool = True) -> Dict:
+    peaks = {}
+    p = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            peaks = json.load(f)
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    timer = _Timer()
+    out = {"metric": "serving tokens/s, hybrid (Fomalix) vs Llama stack of equal size", "dtype": "bf16",
+           "data": "synthetic", "weights": "random", "hbm_gbs_denominator": hbm,
+           "denominator_source": "measured" if peaks else "fallback", "l2": "256 MB buffer rewritten between forwards",
+           "sizes": {}}
+    for name in sizes:
+        z = SIZES[name]
+        entry = {"config": z,
+                 "fomalix": engine_throughput(build_hybrid, z, prefill, batch, context, steps, warmup, timer),
+                 "llama": engine_throughput(build_llama, z, prefill, batch, context, steps, warmup, timer)}
+        if kernels:
+            entry["kernels"] = kernel_table(z, prefill, batch, context, timer, hbm)
+        out["sizes"][name] = entry
+    return out

@@ -112,9 +112,12 @@ def _attend(q, k, v, sink, scale, chunk, block_size, pos0=0):
         vc[order[j // block_size], j % block_size] = v[j]
     tables = order.to(torch.int32)[None].contiguous()
     pos = torch.arange(pos0, pos0 + Tq, dtype=torch.int32)
+    atoms, n_long = None, 0
+    if 16 < Tq <= 128 and d % 4 == 0 and dv % 4 == 0:         # a prompt portion: the tiled kernel where there is one
+        atoms, n_long = torch.tensor([[0, 0, Tq, pos0, 0, pos0 + Tq]], dtype=torch.int32, device=DEV), 1
     out = M.sink_attention(q.to(DEV).contiguous(), kc.to(DEV), vc.to(DEV), None if sink is None else sink.to(DEV),
                            torch.zeros(Tq, dtype=torch.int32, device=DEV), pos.to(DEV), tables.to(DEV), scale, chunk,
-                           torch.float32)
+                           torch.float32, atoms, n_long)
     return out.cpu().view(Tq, Hq, dv)
 
 
@@ -123,11 +126,11 @@ def test_attention_sees_exactly_its_chunk(chunk, block_size):
     """Value j is the one-hot of j, so the output of a query IS its attention weights.  One key just inside and one just
     outside each query's chunk get a score far above the rest: the inside one must take nearly all the weight, the
     outside one none, also where the edge falls on a page border, for whole prompts and for single decode tokens."""
-    T, d = 37, 8
+    T, d = 40, 8
     k = torch.zeros(T, 1, d)
     k[:, 0, 0] = 1.0
     v = torch.eye(T).view(T, 1, T)
-    for i in (0, 1, chunk - 1, chunk, chunk + 1, 2 * chunk, 23, 36):
+    for i in (0, 1, chunk - 1, chunk, chunk + 1, 2 * chunk, 23, 39):
         if i < 0 or i >= T:
             continue
         lo = (i // chunk) * chunk if chunk else 0
