@@ -296,18 +296,37 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
   }
 }
 
-// One warp per (token, query head).  Keys lo..pos of the token's sequence, lo = start of the token's chunk
-// (chunk > 0) or 0.  The softmax denominator starts from exp(sink[h]): a logit without a key or a value.
+// One CTA of 4 warps per (token, query head): single decode tokens and short portions.  Keys lo..pos of the token's
+// sequence, lo = start of the token's chunk (chunk > 0) or 0; the warps take 32-key tiles in turn (a lane scores one
+// key, 16-byte loads of its row; then the tile's weights are broadcast and the lanes hold the value channels) and
+// their partial (max, sum, weighted values) are merged in shared memory.  The softmax denominator also holds
+// exp(sink[h]): a logit without a key or a value.
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int d, bool vec) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (vec) {
+    for (int c = 0; c < d; c += 8) {
+      const float4 x = load4_f32<T>(k + c), y = load4_f32<T>(k + c + 4);
+      a0 += q[c] * x.x + q[c + 4] * y.x;
+      a1 += q[c + 1] * x.y + q[c + 5] * y.y;
+      a2 += q[c + 2] * x.z + q[c + 6] * y.z;
+      a3 += q[c + 3] * x.w + q[c + 7] * y.w;
+    }
+  } else {
+    for (int c = 0; c < d; ++c) a0 += q[c] * to_f32<T>(k[c]);
+  }
+  return (a0 + a1) + (a2 + a3);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                       const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
                       const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
                       int Hq, int G, int d, int dv, float scale, int chunk, const int* __restrict__ atoms) {
-  extern __shared__ float qs[];      // [warps][d]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int h = blockIdx.y * nw + warp;
-  if (h >= Hq) return;
+  extern __shared__ __align__(16) float qs[];      // q [d8] | partial values [4][dv] | partial max [4] | partial sum [4]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
   int t = blockIdx.x, pos, seq;
   if (atoms != nullptr) {            // tokens of short atoms: kShortAtom grid slots per atom
     const int* a = atoms + 6 * (blockIdx.x / kShortAtom);
@@ -317,33 +336,33 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
   } else {
     pos = tok_pos[t], seq = tok_seq[t];
   }
-  float* myq = qs + warp * d;
-  for (int c = lane; c < d; c += 32) myq[c] = q[((long long)t * Hq + h) * d + c];
-  __syncwarp();
+  const int d8 = (d + 7) & ~7;
+  float* pacc = qs + d8;
+  float* pm = pacc + 4 * dv;
+  float* pl = pm + 4;
+  for (int c = threadIdx.x; c < d8; c += blockDim.x) qs[c] = c < d ? q[((long long)t * Hq + h) * d + c] * scale : 0.f;
+  __syncthreads();
   const int g = h / (Hq / G);
   const int* tab = tables + (long long)seq * max_blocks;
   const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
-  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
+  const bool kvec = d % 8 == 0, vvec = dv % 4 == 0;
+  float m = -INFINITY, l = 0.f;
   float acc[kMaxVPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxVPerLane; ++i) acc[i] = 0.f;
-  for (int j0 = lo; j0 <= pos; j0 += 32) {
+  for (int j0 = lo + warp * 32; j0 <= pos; j0 += 128) {
     const int j = j0 + lane;
     float s = -INFINITY;
     if (j <= pos) {
       const long long slot = (long long)tab[j / block_size] * block_size + j % block_size;
-      const T* kr = kcache + (slot * G + g) * d;
-      float a = 0.f;
-      for (int c = 0; c < d; ++c) a += myq[c] * to_f32<T>(kr[c]);
-      s = a * scale;
+      s = dot_row<T>(qs, kcache + (slot * G + g) * d, d, kvec);
     }
-    const float mt = warp_max(s);
-    const float mn = fmaxf(m, mt);
-    const float corr = expf(m - mn);     // m is finite or (no sink, first tile) -inf with l = 0 and acc = 0
+    const float mn = fmaxf(m, warp_max(s));          // finite: the tile holds at least key j0
+    const float corr = expf(m - mn);                 // 0 on the first tile (m = -inf)
     const float p = (j <= pos) ? expf(s - mn) : 0.f;
-    l = l * (m == -INFINITY ? 0.f : corr) + warp_sum(p);
+    l = l * corr + warp_sum(p);
 #pragma unroll
-    for (int i = 0; i < kMaxVPerLane; ++i) acc[i] *= (m == -INFINITY ? 0.f : corr);
+    for (int i = 0; i < kMaxVPerLane; ++i) acc[i] *= corr;
     m = mn;
     const int n = min(32, pos - j0 + 1);
     for (int jj = 0; jj < n; ++jj) {
@@ -351,18 +370,45 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
       const int jk = j0 + jj;
       const long long slot = (long long)tab[jk / block_size] * block_size + jk % block_size;
       const T* vr = vcache + (slot * G + g) * dv;
+      if (vvec) {                                    // lane holds channels 128 i + 4 lane .. + 3
 #pragma unroll
-      for (int i = 0; i < kMaxVPerLane; ++i) {
-        const int c = lane + 32 * i;
-        if (c < dv) acc[i] += pj * to_f32<T>(vr[c]);
+        for (int i = 0; i < kMaxVPerLane / 4; ++i) {
+          const int c = 128 * i + 4 * lane;
+          if (c < dv) {
+            const float4 v = load4_f32<T>(vr + c);
+            acc[4 * i] += pj * v.x, acc[4 * i + 1] += pj * v.y, acc[4 * i + 2] += pj * v.z, acc[4 * i + 3] += pj * v.w;
+          }
+        }
+      } else {                                       // lane holds channels lane + 32 i
+#pragma unroll
+        for (int i = 0; i < kMaxVPerLane; ++i) {
+          const int c = lane + 32 * i;
+          if (c < dv) acc[i] += pj * to_f32<T>(vr[c]);
+        }
       }
     }
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  if (lane == 0) pm[warp] = m, pl[warp] = l;
 #pragma unroll
   for (int i = 0; i < kMaxVPerLane; ++i) {
-    const int c = lane + 32 * i;
-    if (c < dv) out[((long long)t * Hq + h) * dv + c] = from_f32<T>(acc[i] * inv);
+    const int c = vvec ? 128 * (i >> 2) + 4 * lane + (i & 3) : lane + 32 * i;
+    if (c < dv) pacc[warp * dv + c] = acc[i];
+  }
+  __syncthreads();
+  float M = sink ? sink[h] : -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) M = fmaxf(M, pm[w]);
+  float L = sink ? expf(sink[h] - M) : 0.f;
+  float f[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    f[w] = pm[w] == -INFINITY ? 0.f : expf(pm[w] - M);
+    L += pl[w] * f[w];
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    const float o = pacc[c] * f[0] + pacc[dv + c] * f[1] + pacc[2 * dv + c] * f[2] + pacc[3 * dv + c] * f[3];
+    out[((long long)t * Hq + h) * dv + c] = from_f32<T>(o * inv);
   }
 }
 
@@ -661,16 +707,16 @@ SXB_API int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, 
 
 /* Attention of every token over the cached keys lo..pos of its sequence (lo = start of its chunk of `chunk` positions,
  * or 0 when chunk == 0), scores and weights in fp32; sink (fp32 [Hq] or null) adds exp(sink[h]) to the denominator.
- * out `dtype` [n_tokens, Hq * dv].  One warp per (token, head). */
+ * out `dtype` [n_tokens, Hq * dv] (the caches have the same type).  One CTA per (token, head). */
 SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
                                int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
                                int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
   if (dv > 32 * kMaxVPerLane || Hq % G) return SXB_ERR_UNSUPPORTED;
-  const int warps = 4;
-  dim3 grid(n_tokens, (Hq + warps - 1) / warps);
-  SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, warps * 32, warps * d * sizeof(float), (cudaStream_t)stream>>>(
+  dim3 grid(n_tokens, Hq);
+  const size_t smem = (size_t)(((d + 7) & ~7) + 4 * dv + 8) * sizeof(float);
+  SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, 128, smem, (cudaStream_t)stream>>>(
                              (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out,
                              (const int*)tok_seq, (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq,
                              G, d, dv, scale, chunk, nullptr)));
@@ -717,10 +763,10 @@ SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const vo
     SXB_CHECK_LAUNCH();
   }
   if (n_atoms > n_long) {
-    const int warps = 4;
-    dim3 grid((n_atoms - n_long) * kShortAtom, (Hq + warps - 1) / warps);
+    dim3 grid((n_atoms - n_long) * kShortAtom, Hq);
     const int* rest = (const int*)atoms + 6 * n_long;
-    SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, warps * 32, warps * d * sizeof(float), s>>>(
+    const size_t smem = (size_t)(((d + 7) & ~7) + 4 * dv + 8) * sizeof(float);
+    SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, 128, smem, s>>>(
                                (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, nullptr,
                                nullptr, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, rest)));
     SXB_CHECK_LAUNCH();

@@ -136,6 +136,8 @@ def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
     T, Hq, d = q.shape
     bs, G, dv = kcache.shape[1], kcache.shape[2], vcache.shape[3]
     if q.is_cuda:
+        if kcache.dtype != out_dtype or vcache.dtype != out_dtype:
+            raise ValueError("the caches and the output share one activation dtype")
         out = torch.empty(T, Hq * dv, dtype=out_dtype, device=q.device)
         if atoms is not None and n_long > 0 and tiles_supported(d, dv):
             _lib.call("sxb_sink_attention_atoms", q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), _lib.ptr(sink),
