@@ -296,9 +296,9 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
   }
 }
 
-// One CTA of 4 warps per (token, query head): single decode tokens and short portions.  Keys lo..pos of the token's
+// One CTA of kAW warps per (token, key/value head): single decode tokens and short portions.  Keys lo..pos of the token's
 // sequence, lo = start of the token's chunk (chunk > 0) or 0; the warps take 32-key tiles in turn (a lane scores one
-// key, 16-byte loads of its row; then the tile's weights are broadcast and the lanes hold the value channels) and
+// key, whose row reaches it through a coalesced copy into shared memory; then the tile's weights are broadcast and the lanes hold the value channels) and
 // their partial (max, sum, weighted values) are merged in shared memory.  The softmax denominator also holds
 // exp(sink[h]): a logit without a key or a value.
 template <typename T>
@@ -318,15 +318,19 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* _
   return (a0 + a1) + (a2 + a3);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(128)
+constexpr int kAW = 8;               // warps of the per-token attention kernel; they take the key tiles in turn
+
+// REP query heads that share one key/value head are handled together: a loaded key or value row serves all of them.
+template <typename T, int REP>
+__global__ void __launch_bounds__(32 * kAW)
 sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                       const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
                       const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
                       int Hq, int G, int d, int dv, float scale, int chunk, const int* __restrict__ atoms) {
-  extern __shared__ __align__(16) float qs[];      // q [d8] | partial values [4][dv] | partial max [4] | partial sum [4]
+  // q [REP][d8] | partial values [kAW][REP][dv] | partial max [kAW][REP] | partial sum [kAW][REP] | key staging
+  extern __shared__ __align__(16) float qs[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y;
+  const int h0 = blockIdx.y * REP;
   int t = blockIdx.x, pos, seq;
   if (atoms != nullptr) {            // tokens of short atoms: kShortAtom grid slots per atom
     const int* a = atoms + 6 * (blockIdx.x / kShortAtom);
@@ -337,79 +341,174 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
     pos = tok_pos[t], seq = tok_seq[t];
   }
   const int d8 = (d + 7) & ~7;
-  float* pacc = qs + d8;
-  float* pm = pacc + 4 * dv;
-  float* pl = pm + 4;
-  for (int c = threadIdx.x; c < d8; c += blockDim.x) qs[c] = c < d ? q[((long long)t * Hq + h) * d + c] * scale : 0.f;
+  float* pacc = qs + REP * d8;
+  float* pm = pacc + kAW * REP * dv;
+  float* pl = pm + kAW * REP;
+  float* stage = pl + kAW * REP;                 // [kAW warps][32 keys][64 + pad] of T, 16-byte aligned
+  for (int i = threadIdx.x; i < REP * d8; i += blockDim.x) {
+    const int hh = i / d8, c = i % d8;
+    qs[i] = c < d ? q[((long long)t * Hq + h0 + hh) * d + c] * scale : 0.f;
+  }
   __syncthreads();
-  const int g = h / (Hq / G);
+  const int g = h0 / (Hq / G);
   const int* tab = tables + (long long)seq * max_blocks;
   const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
   const bool kvec = d % 8 == 0, vvec = dv % 4 == 0;
-  float m = -INFINITY, l = 0.f;
-  float acc[kMaxVPerLane];
+  float m[REP], l[REP], acc[REP][kMaxVPerLane];
 #pragma unroll
-  for (int i = 0; i < kMaxVPerLane; ++i) acc[i] = 0.f;
-  for (int j0 = lo + warp * 32; j0 <= pos; j0 += 128) {
+  for (int hh = 0; hh < REP; ++hh) {
+    m[hh] = -INFINITY, l[hh] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVPerLane; ++i) acc[hh][i] = 0.f;
+  }
+  for (int j0 = lo + warp * 32; j0 <= pos; j0 += 32 * kAW) {
     const int j = j0 + lane;
-    float s = -INFINITY;
-    if (j <= pos) {
-      const long long slot = (long long)tab[j / block_size] * block_size + j % block_size;
-      s = dot_row<T>(qs, kcache + (slot * G + g) * d, d, kvec);
-    }
-    const float mn = fmaxf(m, warp_max(s));          // finite: the tile holds at least key j0
-    const float corr = expf(m - mn);                 // 0 on the first tile (m = -inf)
-    const float p = (j <= pos) ? expf(s - mn) : 0.f;
-    l = l * corr + warp_sum(p);
-#pragma unroll
-    for (int i = 0; i < kMaxVPerLane; ++i) acc[i] *= corr;
-    m = mn;
     const int n = min(32, pos - j0 + 1);
-    for (int jj = 0; jj < n; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const int jk = j0 + jj;
-      const long long slot = (long long)tab[jk / block_size] * block_size + jk % block_size;
-      const T* vr = vcache + (slot * G + g) * dv;
-      if (vvec) {                                    // lane holds channels 128 i + 4 lane .. + 3
+    const long long myslot = j <= pos ? (long long)tab[j / block_size] * block_size + j % block_size : -1;
+    float sc[REP];
 #pragma unroll
-        for (int i = 0; i < kMaxVPerLane / 4; ++i) {
-          const int c = 128 * i + 4 * lane;
-          if (c < dv) {
-            const float4 v = load4_f32<T>(vr + c);
-            acc[4 * i] += pj * v.x, acc[4 * i + 1] += pj * v.y, acc[4 * i + 2] += pj * v.z, acc[4 * i + 3] += pj * v.w;
+    for (int hh = 0; hh < REP; ++hh) sc[hh] = 0.f;
+    if (kvec) {
+      // the tile's rows come in coalesced, 64 channels at a time, through a padded per-warp buffer; then every lane
+      // reads its own row from there
+      constexpr int E = 16 / (int)sizeof(T), SP = 64 + E;
+      T* st = reinterpret_cast<T*>(stage) + warp * 32 * SP;
+      for (int c0 = 0; c0 < d; c0 += 64) {
+        const int w = min(64, d - c0), per = w / E;
+        for (int i = lane; i < 32 * per; i += 32) {
+          const int r = i / per, cc = (i % per) * E;
+          const long long slot = __shfl_sync(0xffffffffu, myslot, r);
+          uint4 u = make_uint4(0u, 0u, 0u, 0u);
+          if (slot >= 0) u = *reinterpret_cast<const uint4*>(kcache + (slot * G + g) * d + c0 + cc);
+          *reinterpret_cast<uint4*>(st + r * SP + cc) = u;
+        }
+        __syncwarp();
+        for (int cc = 0; cc < w; cc += 4) {
+          const float4 x = load4_f32<T>(st + lane * SP + cc);
+#pragma unroll
+          for (int hh = 0; hh < REP; ++hh) {
+            const float4 y = *reinterpret_cast<const float4*>(qs + hh * d8 + c0 + cc);
+            sc[hh] += (y.x * x.x + y.y * x.y) + (y.z * x.z + y.w * x.w);
           }
         }
-      } else {                                       // lane holds channels lane + 32 i
+        __syncwarp();
+      }
+    } else if (j <= pos) {
 #pragma unroll
-        for (int i = 0; i < kMaxVPerLane; ++i) {
-          const int c = lane + 32 * i;
-          if (c < dv) acc[i] += pj * to_f32<T>(vr[c]);
+      for (int hh = 0; hh < REP; ++hh) sc[hh] = dot_row<T>(qs + hh * d8, kcache + (myslot * G + g) * d, d, false);
+    }
+    float p[REP];
+#pragma unroll
+    for (int hh = 0; hh < REP; ++hh) {
+      const float s = j <= pos ? sc[hh] : -INFINITY;
+      const float mn = fmaxf(m[hh], warp_max(s));      // finite: the tile holds at least key j0
+      const float corr = expf(m[hh] - mn);             // 0 on the first tile (m = -inf)
+      p[hh] = (j <= pos) ? expf(s - mn) : 0.f;
+      l[hh] = l[hh] * corr + warp_sum(p[hh]);
+#pragma unroll
+      for (int i = 0; i < kMaxVPerLane; ++i) acc[hh][i] *= corr;
+      m[hh] = mn;
+    }
+    if (vvec) {                                      // lane holds channels 128 i + 4 lane .. + 3; 4 keys in flight
+      for (int jj = 0; jj < n; jj += 4) {
+        float4 v[4][kMaxVPerLane / 4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long slot = __shfl_sync(0xffffffffu, myslot, min(jj + u, n - 1));
+          const T* vr = vcache + (slot * G + g) * dv;
+#pragma unroll
+          for (int i = 0; i < kMaxVPerLane / 4; ++i) {
+            const int c = 128 * i + 4 * lane;
+            v[u][i] = c < dv ? load4_f32<T>(vr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int hh = 0; hh < REP; ++hh) {
+            const float pj = __shfl_sync(0xffffffffu, p[hh], (jj + u) & 31);      // 0 beyond the last key
+#pragma unroll
+            for (int i = 0; i < kMaxVPerLane / 4; ++i) {
+              acc[hh][4 * i] += pj * v[u][i].x, acc[hh][4 * i + 1] += pj * v[u][i].y;
+              acc[hh][4 * i + 2] += pj * v[u][i].z, acc[hh][4 * i + 3] += pj * v[u][i].w;
+            }
+          }
+      }
+    } else {                                         // lane holds channels lane + 32 i
+      for (int jj = 0; jj < n; ++jj) {
+        const long long slot = __shfl_sync(0xffffffffu, myslot, jj);
+        const T* vr = vcache + (slot * G + g) * dv;
+#pragma unroll
+        for (int hh = 0; hh < REP; ++hh) {
+          const float pj = __shfl_sync(0xffffffffu, p[hh], jj);
+#pragma unroll
+          for (int i = 0; i < kMaxVPerLane; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dv) acc[hh][i] += pj * to_f32<T>(vr[c]);
+          }
         }
       }
     }
   }
-  if (lane == 0) pm[warp] = m, pl[warp] = l;
 #pragma unroll
-  for (int i = 0; i < kMaxVPerLane; ++i) {
-    const int c = vvec ? 128 * (i >> 2) + 4 * lane + (i & 3) : lane + 32 * i;
-    if (c < dv) pacc[warp * dv + c] = acc[i];
+  for (int hh = 0; hh < REP; ++hh) {
+    if (lane == 0) pm[warp * REP + hh] = m[hh], pl[warp * REP + hh] = l[hh];
+#pragma unroll
+    for (int i = 0; i < kMaxVPerLane; ++i) {
+      const int c = vvec ? 128 * (i >> 2) + 4 * lane + (i & 3) : lane + 32 * i;
+      if (c < dv) pacc[(warp * REP + hh) * dv + c] = acc[hh][i];
+    }
   }
   __syncthreads();
-  float M = sink ? sink[h] : -INFINITY;
+  for (int idx = threadIdx.x; idx < REP * dv; idx += blockDim.x) {
+    const int hh = idx / dv, c = idx % dv;
+    float M = sink ? sink[h0 + hh] : -INFINITY;
 #pragma unroll
-  for (int w = 0; w < 4; ++w) M = fmaxf(M, pm[w]);
-  float L = sink ? expf(sink[h] - M) : 0.f;
-  float f[4];
+    for (int w = 0; w < kAW; ++w) M = fmaxf(M, pm[w * REP + hh]);
+    float L = sink ? expf(sink[h0 + hh] - M) : 0.f, o = 0.f;
 #pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    f[w] = pm[w] == -INFINITY ? 0.f : expf(pm[w] - M);
-    L += pl[w] * f[w];
+    for (int w = 0; w < kAW; ++w) {
+      const float f = pm[w * REP + hh] == -INFINITY ? 0.f : expf(pm[w * REP + hh] - M);
+      L += pl[w * REP + hh] * f;
+      o += pacc[(w * REP + hh) * dv + c] * f;
+    }
+    out[((long long)t * Hq + h0 + hh) * dv + c] = from_f32<T>(L > 0.f ? o / L : 0.f);
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
-  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
-    const float o = pacc[c] * f[0] + pacc[dv + c] * f[1] + pacc[2 * dv + c] * f[2] + pacc[3 * dv + c] * f[3];
-    out[((long long)t * Hq + h) * dv + c] = from_f32<T>(o * inv);
-  }
+}
+
+template <typename T, int REP>
+static int launch_attention_rows(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
+                                 void* out, const void* tok_seq, const void* tok_pos, const void* tables,
+                                 int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
+                                 const int* atoms, cudaStream_t s) {
+  const size_t smem = (size_t)(REP * ((d + 7) & ~7) + kAW * REP * dv + 2 * kAW * REP + kAW * 32 * 68) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(sink_attention_kernel<T, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  grid.y = Hq / REP;
+  sink_attention_kernel<T, REP><<<grid, 32 * kAW, smem, s>>>(
+      (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)tok_seq,
+      (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, atoms);
+  return SXB_OK;
+}
+
+// Query heads per key/value head that one CTA takes together: the largest of 8, 4, 2, 1 that divides the group.
+static int attention_rows(int dtype, dim3 grid, const void* q, const void* kcache, const void* vcache,
+                          const void* sink, void* out, const void* tok_seq, const void* tok_pos, const void* tables,
+                          int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
+                          const int* atoms, cudaStream_t s) {
+  const int group = Hq / G;
+  int rc = SXB_OK;
+#define ROWS(REP)                                                                                                      \
+  SEQMIX_DISPATCH(dtype, (rc = launch_attention_rows<T, REP>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos,      \
+                                                              tables, max_blocks, block_size, Hq, G, d, dv, scale,      \
+                                                              chunk, atoms, s)))
+  if (group % 8 == 0) ROWS(8);
+  else if (group % 4 == 0) ROWS(4);
+  else if (group % 2 == 0) ROWS(2);
+  else ROWS(1);
+#undef ROWS
+  return rc;
 }
 
 // ------------------------------------------------------------------------------------------------ short convolution
@@ -714,12 +813,9 @@ SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vc
                                int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
   if (dv > 32 * kMaxVPerLane || Hq % G) return SXB_ERR_UNSUPPORTED;
-  dim3 grid(n_tokens, Hq);
-  const size_t smem = (size_t)(((d + 7) & ~7) + 4 * dv + 8) * sizeof(float);
-  SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, 128, smem, (cudaStream_t)stream>>>(
-                             (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out,
-                             (const int*)tok_seq, (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq,
-                             G, d, dv, scale, chunk, nullptr)));
+  const int rc = attention_rows(dtype, dim3(n_tokens, 1), q, kcache, vcache, sink, out, tok_seq, tok_pos, tables,
+                                max_blocks, block_size, Hq, G, d, dv, scale, chunk, nullptr, (cudaStream_t)stream);
+  if (rc != SXB_OK) return rc;
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }
@@ -763,12 +859,10 @@ SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const vo
     SXB_CHECK_LAUNCH();
   }
   if (n_atoms > n_long) {
-    dim3 grid((n_atoms - n_long) * kShortAtom, Hq);
-    const int* rest = (const int*)atoms + 6 * n_long;
-    const size_t smem = (size_t)(((d + 7) & ~7) + 4 * dv + 8) * sizeof(float);
-    SEQMIX_DISPATCH(dtype, (sink_attention_kernel<T><<<grid, 128, smem, s>>>(
-                               (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, nullptr,
-                               nullptr, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, rest)));
+    const int rc = attention_rows(dtype, dim3((n_atoms - n_long) * kShortAtom, 1), q, kcache, vcache, sink, out, nullptr,
+                                  nullptr, tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk,
+                                  (const int*)atoms + 6 * n_long, s);
+    if (rc != SXB_OK) return rc;
     SXB_CHECK_LAUNCH();
   }
   return SXB_OK;
