@@ -601,39 +601,57 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
                          const float* __restrict__ beta, const float* __restrict__ skip, float* __restrict__ state,
                          float* __restrict__ out, const int* __restrict__ seq_info, int H, int G, int n, int dv,
                          int delta) {
-  // two staging buffers, each k [TB][n] | q [TB][n] | v [TB][kCols] | decay [TB] | beta [TB]: the next TB tokens are
-  // copied in (cp.async) while the current ones are walked
-  extern __shared__ float sm[];
-  const int stage = 2 * kTB * n + kTB * kCols + 2 * kTB;
+  // Lane l of a column holds the float4 chunks l, l + 8, l + 16, ... of the column's n-vector (padded with zeros to
+  // NP = 8 R), so k, q and the state move as 16-byte words without bank conflicts.  Two staging buffers, each
+  // k [TB][NP] | q [TB][NP] | v [TB][kCols] | decay [TB] | beta [TB]: the next TB tokens are copied in (cp.async) while
+  // the current ones are walked.
+  constexpr int NP = R * kLPC, R4 = R / 4;
+  extern __shared__ __align__(16) float sm[];
+  constexpr int stage = 2 * kTB * NP + kTB * kCols + 2 * kTB;
   const int* si = seq_info + 4 * blockIdx.z;
   const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
   const int h = blockIdx.y, g = h / (H / G);
   const int lc = threadIdx.x / kLPC, l = threadIdx.x % kLPC;
   const int col = blockIdx.x * kCols + lc;
   const bool live = col < dv;
+  for (int i = threadIdx.x; i < 2 * stage; i += blockDim.x) sm[i] = 0.f;      // the padding stays zero
   float* sp = state + (((long long)slot * H + h) * dv + (live ? col : 0)) * n;
+  const bool n4 = (n & 3) == 0;
   float S[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = l + kLPC * r;
-    S[r] = (live && seen > 0 && i < n) ? sp[i] : 0.f;
+  for (int r4 = 0; r4 < R4; ++r4) {
+    const int i = (r4 * kLPC + l) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && seen > 0) {
+      if (n4 && i < n) {
+        v = *reinterpret_cast<const float4*>(sp + i);
+      } else {
+        if (i < n) v.x = sp[i];
+        if (i + 1 < n) v.y = sp[i + 1];
+        if (i + 2 < n) v.z = sp[i + 2];
+        if (i + 3 < n) v.w = sp[i + 3];
+      }
+    }
+    S[4 * r4] = v.x, S[4 * r4 + 1] = v.y, S[4 * r4 + 2] = v.z, S[4 * r4 + 3] = v.w;
   }
   const float D = skip ? skip[h] : 0.f;
+  __syncthreads();
 
   auto stage_in = [&](int buf, int t0) {
     float* sk = sm + buf * stage;
-    float* sq = sk + kTB * n;
-    float* sv = sq + kTB * n;
+    float* sq = sk + kTB * NP;
+    float* sv = sq + kTB * NP;
     float* sa = sv + kTB * kCols;
     float* sb = sa + kTB;
     const int nt = min(kTB, rows - t0);
     for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
-      const long long row = first + t0 + i / n;
-      __pipeline_memcpy_async(sk + i, kvec + row * ldkq + g * n + i % n, 4);
-      __pipeline_memcpy_async(sq + i, qvec + row * ldkq + g * n + i % n, 4);
+      const int tt = i / n, c = i % n;
+      const long long row = first + t0 + tt;
+      __pipeline_memcpy_async(sk + tt * NP + c, kvec + row * ldkq + g * n + c, 4);
+      __pipeline_memcpy_async(sq + tt * NP + c, qvec + row * ldkq + g * n + c, 4);
     }
     for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
-      const int c = min(blockIdx.x * kCols + i % kCols, dv - 1);
+      const int c = min((int)blockIdx.x * kCols + i % kCols, dv - 1);
       __pipeline_memcpy_async(sv + i, val + (long long)(first + t0 + i / kCols) * ldv + h * dv + c, 4);
     }
     for (int i = threadIdx.x; i < nt; i += blockDim.x) {
@@ -653,43 +671,39 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     else __pipeline_wait_prior(0);
     __syncthreads();
     const float* sk = sm + buf * stage;
-    const float* sq = sk + kTB * n;
-    const float* sv = sq + kTB * n;
+    const float* sq = sk + kTB * NP;
+    const float* sv = sq + kTB * NP;
     const float* sa = sv + kTB * kCols;
     const float* sb = sa + kTB;
     for (int tt = 0; tt < nt; ++tt) {
       const float a = sa[tt], b = sb[tt], v = sv[tt * kCols + lc];
-      const float* kk = sk + tt * n;
-      const float* qq = sq + tt * n;
+      const float4* kk = reinterpret_cast<const float4*>(sk + tt * NP) + l;
+      const float4* qq = reinterpret_cast<const float4*>(sq + tt * NP) + l;
+      float4 k4[R4];
+#pragma unroll
+      for (int r4 = 0; r4 < R4; ++r4) k4[r4] = kk[r4 * kLPC];
       float u = b * v;
-      if (delta) {
+      if (delta) {                     // (a S)^T k = a (S^T k): the decay is folded into the update below
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-        for (int r = 0; r < R; r += 4) {
-          S[r] *= a, S[r + 1] *= a, S[r + 2] *= a, S[r + 3] *= a;
-          const int i = l + kLPC * r;
-          if (i < n) d0 += S[r] * kk[i];
-          if (i + kLPC < n) d1 += S[r + 1] * kk[i + kLPC];
-          if (i + 2 * kLPC < n) d2 += S[r + 2] * kk[i + 2 * kLPC];
-          if (i + 3 * kLPC < n) d3 += S[r + 3] * kk[i + 3 * kLPC];
+        for (int r4 = 0; r4 < R4; ++r4) {
+          d0 += S[4 * r4] * k4[r4].x, d1 += S[4 * r4 + 1] * k4[r4].y;
+          d2 += S[4 * r4 + 2] * k4[r4].z, d3 += S[4 * r4 + 3] * k4[r4].w;
         }
         float dot = (d0 + d1) + (d2 + d3);
         dot += __shfl_xor_sync(0xffffffffu, dot, 1);
         dot += __shfl_xor_sync(0xffffffffu, dot, 2);
         dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-        u = b * (v - dot);
-      } else {
-#pragma unroll
-        for (int r = 0; r < R; ++r) S[r] *= a;
+        u = b * (v - a * dot);
       }
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        const int i = l + kLPC * r;
-        if (i < n) S[r] += kk[i] * u, o0 += S[r] * qq[i];
-        if (i + kLPC < n) S[r + 1] += kk[i + kLPC] * u, o1 += S[r + 1] * qq[i + kLPC];
-        if (i + 2 * kLPC < n) S[r + 2] += kk[i + 2 * kLPC] * u, o2 += S[r + 2] * qq[i + 2 * kLPC];
-        if (i + 3 * kLPC < n) S[r + 3] += kk[i + 3 * kLPC] * u, o3 += S[r + 3] * qq[i + 3 * kLPC];
+      for (int r4 = 0; r4 < R4; ++r4) {
+        const float4 q4 = qq[r4 * kLPC];
+        S[4 * r4] = fmaf(k4[r4].x, u, S[4 * r4] * a), o0 += S[4 * r4] * q4.x;
+        S[4 * r4 + 1] = fmaf(k4[r4].y, u, S[4 * r4 + 1] * a), o1 += S[4 * r4 + 1] * q4.y;
+        S[4 * r4 + 2] = fmaf(k4[r4].z, u, S[4 * r4 + 2] * a), o2 += S[4 * r4 + 2] * q4.z;
+        S[4 * r4 + 3] = fmaf(k4[r4].w, u, S[4 * r4 + 3] * a), o3 += S[4 * r4 + 3] * q4.w;
       }
       float o = (o0 + o1) + (o2 + o3);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
@@ -701,9 +715,16 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
   }
   if (live) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int i = l + kLPC * r;
-      if (i < n) sp[i] = S[r];
+    for (int r4 = 0; r4 < R4; ++r4) {
+      const int i = (r4 * kLPC + l) * 4;
+      if (n4 && i < n) {
+        *reinterpret_cast<float4*>(sp + i) = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]);
+      } else {
+        if (i < n) sp[i] = S[4 * r4];
+        if (i + 1 < n) sp[i + 1] = S[4 * r4 + 1];
+        if (i + 2 < n) sp[i + 2] = S[4 * r4 + 2];
+        if (i + 3 < n) sp[i + 3] = S[4 * r4 + 3];
+      }
     }
   }
 }
@@ -933,7 +954,8 @@ SXB_API int sxb_linear_recurrence(const void* kvec, const void* qvec, long long 
   if (n_seqs <= 0) return SXB_OK;
   if (n > 256 || H % G) return SXB_ERR_UNSUPPORTED;
   dim3 grid((dv + kCols - 1) / kCols, H, n_seqs);
-  const size_t smem = (size_t)2 * (2 * kTB * n + kTB * kCols + 2 * kTB) * sizeof(float);
+  const int np = n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256));
+  const size_t smem = (size_t)2 * (2 * kTB * np + kTB * kCols + 2 * kTB) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
 #define LAUNCH_REC(R)                                                                                              \
   linear_recurrence_kernel<R><<<grid, kLPC * kCols, smem, s>>>(                                                     \
