@@ -60,6 +60,9 @@ def parse():
     ap.add_argument("--serve-prefill", type=int, default=4096)
     ap.add_argument("--serve-batch", type=int, default=64)
     ap.add_argument("--serve-context", type=int, default=2560)
+    ap.add_argument("--serve-chunk", type=int, default=0,
+                    help="chunk size of the hybrid stack's attention mask (default: 4096, one chunk holds the whole "
+                         "prompt, so the attention work equals the Llama stack's)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the secondary measurements (exposed communication, fused-path rooflines, the line at "
                          "the reference's recompute setting)")
@@ -472,7 +475,7 @@ def main():
         from shuffle_exchange_b200.inference.v2 import serve_bench
         sizes = list(serve_bench.SIZES) if args.serve == "all" else args.serve.split(",")
         print(json.dumps(serve_bench.run(sizes, args.serve_prefill, args.serve_batch, args.serve_context, args.steps,
-                                         args.warmup)))
+                                         args.warmup, chunk=args.serve_chunk)))
         return
     if args.impl == "reference":
         try:

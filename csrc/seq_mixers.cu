@@ -15,6 +15,7 @@
 //   linear_recurrence     S <- a S;  u = b (v - [delta] S^T k);  S <- S + k u^T;  o = S^T q (+ D v), state per slot
 //   group_norm_gate       RMS norm over channel groups combined with a SiLU gate (before or after the norm)
 //   gated_act_rows        act(gate) * up for any width and fp32 or bf16 rows
+#include <algorithm>
 #include "sxb_common.cuh"
 #include <cuda_pipeline.h>
 
@@ -151,11 +152,12 @@ __device__ __forceinline__ float4 load4_f32<__nv_bfloat16>(const __nv_bfloat16* 
 }
 
 // Tiled form for atoms of many queries (prompt portions): one CTA per (64 queries of an atom, query head).  Q (scaled),
-// one 64-key tile of K and V (converted to fp32) and the tile's weights sit in shared memory; 256 threads hold 4x4
+// one 64-key tile of K and V (converted to fp32) and the tile's weights (in the key tile's place, once the scores are
+// done: head sizes up to 128 then leave room for two CTAs per SM) sit in shared memory; 256 threads hold 4x4
 // scores and 4 x (dv/16) outputs each.  Scores, online softmax with the sink logit, and the weighted sum are fp32 FMAs:
 // the weights must stay 32-bit, so the products cannot go through the bf16 tensor path.
 template <typename T, int NV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, NV <= 2 ? 2 : 1)
 sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                            const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ atoms,
                            const int* __restrict__ tables, int max_blocks, int block_size, int Hq, int G, int d,
@@ -164,8 +166,8 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
   const int dp = d + 4, vp = NV * 64, pp = kBK + 4;
   float* Qs = smf;
   float* Ks = Qs + kBQ * dp;
-  float* Vs = Ks + kBK * dp;
-  float* Ps = Vs + kBK * vp;
+  float* Vs = Ks + max(kBK * dp, kBQ * pp);
+  float* Ps = Ks;                    // the weights take the key tile's place once every warp has its scores
   const int* a = atoms + 6 * (blockIdx.x >> 1);
   const int sub = blockIdx.x & 1;
   const int nq = min(a[2] - sub * kBQ, kBQ);
@@ -182,13 +184,16 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
     v.x *= scale, v.y *= scale, v.z *= scale, v.w *= scale;
     *reinterpret_cast<float4*>(Qs + r * dp + c) = v;
   }
-  float m[4], l[4], acc[4][NV * 4];
+  // The products run as packed pairs (fma.f32x2: two 32-bit FMAs per lane and instruction), so scores and outputs are
+  // held as float2.
+  float m[4], l[4];
+  float2 acc[4][NV * 2];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     m[i] = sink ? sink[h] : -INFINITY;
     l[i] = sink ? 1.f : 0.f;
 #pragma unroll
-    for (int c = 0; c < NV * 4; ++c) acc[i][c] = 0.f;
+    for (int c = 0; c < NV * 2; ++c) acc[i][c] = make_float2(0.f, 0.f);
   }
   const int last = pos0 + nq - 1;
   const int kbeg = chunk > 0 ? (pos0 / chunk) * chunk : 0;
@@ -213,11 +218,11 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
       *reinterpret_cast<float4*>(Vs + r * vp + c) = v;
     }
     __syncthreads();
-    float s[4][4];
+    float2 s2[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+      for (int j = 0; j < 4; ++j) s2[i][j] = make_float2(0.f, 0.f);
     for (int c = 0; c < d; c += 4) {
       float4 qv[4], kv[4];
 #pragma unroll
@@ -227,9 +232,17 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          s[i][j] += qv[i].x * kv[j].x + qv[i].y * kv[j].y + qv[i].z * kv[j].z + qv[i].w * kv[j].w;
+        for (int j = 0; j < 4; ++j) {
+          s2[i][j] = __ffma2_rn(make_float2(qv[i].x, qv[i].y), make_float2(kv[j].x, kv[j].y), s2[i][j]);
+          s2[i][j] = __ffma2_rn(make_float2(qv[i].z, qv[i].w), make_float2(kv[j].z, kv[j].w), s2[i][j]);
+        }
     }
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = s2[i][j].x + s2[i][j].y;
+    __syncthreads();       // every warp is done with the key tile: its space now holds the weights
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = ty + 16 * i, qp = pos0 + r;
@@ -257,7 +270,7 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
       l[i] = l[i] * corr + ps;
       m[i] = mn;
 #pragma unroll
-      for (int c = 0; c < NV * 4; ++c) acc[i][c] *= corr;
+      for (int c = 0; c < NV * 2; ++c) acc[i][c] = __fmul2_rn(acc[i][c], make_float2(corr, corr));
     }
     __syncwarp();          // a row of weights is written and read by the 16 threads of one half-warp
     for (int j = 0; j < kBK; j += 4) {
@@ -272,10 +285,9 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float p = jj == 0 ? pv[i].x : (jj == 1 ? pv[i].y : (jj == 2 ? pv[i].z : pv[i].w));
-            acc[i][n * 4 + 0] += p * vv.x;
-            acc[i][n * 4 + 1] += p * vv.y;
-            acc[i][n * 4 + 2] += p * vv.z;
-            acc[i][n * 4 + 3] += p * vv.w;
+            const float2 p2 = make_float2(p, p);
+            acc[i][n * 2] = __ffma2_rn(p2, make_float2(vv.x, vv.y), acc[i][n * 2]);
+            acc[i][n * 2 + 1] = __ffma2_rn(p2, make_float2(vv.z, vv.w), acc[i][n * 2 + 1]);
           }
         }
       }
@@ -291,7 +303,8 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int c = n * 64 + tx * 4 + e;
-        if (c < dv) out[((long long)(row0 + r) * Hq + h) * dv + c] = from_f32<T>(acc[i][n * 4 + e] * inv);
+        const float2 a2 = acc[i][n * 2 + (e >> 1)];
+        if (c < dv) out[((long long)(row0 + r) * Hq + h) * dv + c] = from_f32<T>(((e & 1) ? a2.y : a2.x) * inv);
       }
   }
 }
@@ -319,9 +332,12 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* _
 }
 
 constexpr int kAW = 8;               // warps of the per-token attention kernel; they take the key tiles in turn
+constexpr int kKeyLoads = 8;         // 16-byte key loads a lane issues before it stores the first one
+constexpr int kValLoads = 8;         // value rows a warp has in flight
 
 // REP query heads that share one key/value head are handled together: a loaded key or value row serves all of them.
-template <typename T, int REP>
+// VPL: value channels a lane holds (4 for value heads up to 128, else 8).
+template <typename T, int REP, int VPL>
 __global__ void __launch_bounds__(32 * kAW)
 sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                       const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
@@ -354,12 +370,12 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
   const int* tab = tables + (long long)seq * max_blocks;
   const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
   const bool kvec = d % 8 == 0, vvec = dv % 4 == 0;
-  float m[REP], l[REP], acc[REP][kMaxVPerLane];
+  float m[REP], l[REP], acc[REP][VPL];
 #pragma unroll
   for (int hh = 0; hh < REP; ++hh) {
     m[hh] = -INFINITY, l[hh] = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVPerLane; ++i) acc[hh][i] = 0.f;
+    for (int i = 0; i < VPL; ++i) acc[hh][i] = 0.f;
   }
   for (int j0 = lo + warp * 32; j0 <= pos; j0 += 32 * kAW) {
     const int j = j0 + lane;
@@ -375,12 +391,22 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
       T* st = reinterpret_cast<T*>(stage) + warp * 32 * SP;
       for (int c0 = 0; c0 < d; c0 += 64) {
         const int w = min(64, d - c0), per = w / E;
-        for (int i = lane; i < 32 * per; i += 32) {
-          const int r = i / per, cc = (i % per) * E;
-          const long long slot = __shfl_sync(0xffffffffu, myslot, r);
-          uint4 u = make_uint4(0u, 0u, 0u, 0u);
-          if (slot >= 0) u = *reinterpret_cast<const uint4*>(kcache + (slot * G + g) * d + c0 + cc);
-          *reinterpret_cast<uint4*>(st + r * SP + cc) = u;
+        for (int i0 = 0; i0 < per; i0 += kKeyLoads) {          // kKeyLoads 16-byte loads per lane in flight
+          uint4 u[kKeyLoads];
+#pragma unroll
+          for (int x = 0; x < kKeyLoads; ++x) {
+            if (i0 + x >= per) break;
+            const int i = lane + 32 * (i0 + x), r = i / per, cc = (i % per) * E;
+            const long long slot = __shfl_sync(0xffffffffu, myslot, r);
+            u[x] = make_uint4(0u, 0u, 0u, 0u);
+            if (slot >= 0) u[x] = *reinterpret_cast<const uint4*>(kcache + (slot * G + g) * d + c0 + cc);
+          }
+#pragma unroll
+          for (int x = 0; x < kKeyLoads; ++x) {
+            if (i0 + x >= per) break;
+            const int i = lane + 32 * (i0 + x), r = i / per, cc = (i % per) * E;
+            *reinterpret_cast<uint4*>(st + r * SP + cc) = u[x];
+          }
         }
         __syncwarp();
         for (int cc = 0; cc < w; cc += 4) {
@@ -406,29 +432,29 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
       p[hh] = (j <= pos) ? expf(s - mn) : 0.f;
       l[hh] = l[hh] * corr + warp_sum(p[hh]);
 #pragma unroll
-      for (int i = 0; i < kMaxVPerLane; ++i) acc[hh][i] *= corr;
+      for (int i = 0; i < VPL; ++i) acc[hh][i] *= corr;
       m[hh] = mn;
     }
-    if (vvec) {                                      // lane holds channels 128 i + 4 lane .. + 3; 4 keys in flight
-      for (int jj = 0; jj < n; jj += 4) {
-        float4 v[4][kMaxVPerLane / 4];
+    if (vvec) {                                      // lane holds channels 128 i + 4 lane .. + 3; kValLoads keys in flight
+      for (int jj = 0; jj < n; jj += kValLoads) {
+        float4 v[kValLoads][VPL / 4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kValLoads; ++u) {
           const long long slot = __shfl_sync(0xffffffffu, myslot, min(jj + u, n - 1));
           const T* vr = vcache + (slot * G + g) * dv;
 #pragma unroll
-          for (int i = 0; i < kMaxVPerLane / 4; ++i) {
+          for (int i = 0; i < VPL / 4; ++i) {
             const int c = 128 * i + 4 * lane;
             v[u][i] = c < dv ? load4_f32<T>(vr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < kValLoads; ++u)
 #pragma unroll
           for (int hh = 0; hh < REP; ++hh) {
             const float pj = __shfl_sync(0xffffffffu, p[hh], (jj + u) & 31);      // 0 beyond the last key
 #pragma unroll
-            for (int i = 0; i < kMaxVPerLane / 4; ++i) {
+            for (int i = 0; i < VPL / 4; ++i) {
               acc[hh][4 * i] += pj * v[u][i].x, acc[hh][4 * i + 1] += pj * v[u][i].y;
               acc[hh][4 * i + 2] += pj * v[u][i].z, acc[hh][4 * i + 3] += pj * v[u][i].w;
             }
@@ -442,7 +468,7 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
         for (int hh = 0; hh < REP; ++hh) {
           const float pj = __shfl_sync(0xffffffffu, p[hh], jj);
 #pragma unroll
-          for (int i = 0; i < kMaxVPerLane; ++i) {
+          for (int i = 0; i < VPL; ++i) {
             const int c = lane + 32 * i;
             if (c < dv) acc[hh][i] += pj * to_f32<T>(vr[c]);
           }
@@ -454,7 +480,7 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
   for (int hh = 0; hh < REP; ++hh) {
     if (lane == 0) pm[warp * REP + hh] = m[hh], pl[warp * REP + hh] = l[hh];
 #pragma unroll
-    for (int i = 0; i < kMaxVPerLane; ++i) {
+    for (int i = 0; i < VPL; ++i) {
       const int c = vvec ? 128 * (i >> 2) + 4 * lane + (i & 3) : lane + 32 * i;
       if (c < dv) pacc[(warp * REP + hh) * dv + c] = acc[hh][i];
     }
@@ -476,20 +502,32 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
   }
 }
 
+template <typename T, int REP, int VPL>
+static int launch_attention_rows_v(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
+                                   void* out, const void* tok_seq, const void* tok_pos, const void* tables,
+                                   int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale,
+                                   int chunk, const int* atoms, cudaStream_t s) {
+  const size_t smem = (size_t)(REP * ((d + 7) & ~7) + kAW * REP * dv + 2 * kAW * REP + kAW * 32 * 68) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(sink_attention_kernel<T, REP, VPL>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  grid.y = Hq / REP;
+  sink_attention_kernel<T, REP, VPL><<<grid, 32 * kAW, smem, s>>>(
+      (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)tok_seq,
+      (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, atoms);
+  return SXB_OK;
+}
+
 template <typename T, int REP>
 static int launch_attention_rows(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
                                  void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                                  int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
                                  const int* atoms, cudaStream_t s) {
-  const size_t smem = (size_t)(REP * ((d + 7) & ~7) + kAW * REP * dv + 2 * kAW * REP + kAW * 32 * 68) * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(sink_attention_kernel<T, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  grid.y = Hq / REP;
-  sink_attention_kernel<T, REP><<<grid, 32 * kAW, smem, s>>>(
-      (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)tok_seq,
-      (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, atoms);
-  return SXB_OK;
+  if (dv <= 128)
+    return launch_attention_rows_v<T, REP, 4>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos, tables, max_blocks,
+                                              block_size, Hq, G, d, dv, scale, chunk, atoms, s);
+  return launch_attention_rows_v<T, REP, kMaxVPerLane>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos, tables,
+                                                       max_blocks, block_size, Hq, G, d, dv, scale, chunk, atoms, s);
 }
 
 // Query heads per key/value head that one CTA takes together: the largest of 8, 4, 2, 1 that divides the group.
@@ -590,37 +628,40 @@ recurrence_gates_kernel(const T* __restrict__ a_raw, const T* __restrict__ b_raw
 // ------------------------------------------------------------------------------------------------ recurrence
 // State per (slot, head): dv columns of n floats, stored [dv][n].  Each output column evolves on its own:
 //   s <- a s;  u = b (v_c - [delta] s.k);  s <- s + k u;  o_c = s.q (+ D v_c)
-// A column is held by LPC = 8 lanes (n split i = lane + 8 r), 16 columns per CTA; the CTA walks its sequence's rows in
-// order, staging k and q of TB tokens at a time in shared memory.
-constexpr int kLPC = 8, kCols = 16, kTB = 8;
+// A column is held by LPC = 8 lanes (the n-vector as 16-byte chunks, chunk i on lane i mod LPC), 128 / LPC columns per
+// CTA; the CTA walks its sequence's rows in order, staging k and q of TB tokens at a time in shared memory.  (Spreading
+// a column over a whole warp gives a long sequence four times as many warps, but was measured slower: the work per SM
+// is the same and the longer shuffle trees add instructions.)  The products run as packed pairs (fma.f32x2).
+constexpr int kRecThreads = 128, kTB = 8;
 
-template <int R>
-__global__ void __launch_bounds__(kLPC* kCols)
+template <int R, bool DELTA, int LPC>
+__global__ void __launch_bounds__(kRecThreads)
 linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict__ qvec, long long ldkq,
                          const float* __restrict__ val, long long ldv, const float* __restrict__ decay,
                          const float* __restrict__ beta, const float* __restrict__ skip, float* __restrict__ state,
-                         float* __restrict__ out, const int* __restrict__ seq_info, int H, int G, int n, int dv,
-                         int delta) {
-  // Lane l of a column holds the float4 chunks l, l + 8, l + 16, ... of the column's n-vector (padded with zeros to
-  // NP = 8 R), so k, q and the state move as 16-byte words without bank conflicts.  Two staging buffers, each
-  // k [TB][NP] | q [TB][NP] | v [TB][kCols] | decay [TB] | beta [TB]: the next TB tokens are copied in (cp.async) while
+                         float* __restrict__ out, const int* __restrict__ seq_info, int H, int G, int n, int dv) {
+  // Lane l of a column holds the float4 chunks l, l + LPC, l + 2 LPC, ... of the column's n-vector (padded with zeros
+  // to NP = LPC R), so k, q and the state move as 16-byte words without bank conflicts.  Two staging buffers, each
+  // k [TB][NP] | q [TB][NP] | v [TB][COLS] | decay [TB] | beta [TB]: the next TB tokens are copied in (cp.async) while
   // the current ones are walked.
-  constexpr int NP = R * kLPC, R4 = R / 4;
+  constexpr int NP = R * LPC, R4 = R / 4, COLS = kRecThreads / LPC;
   extern __shared__ __align__(16) float sm[];
-  constexpr int stage = 2 * kTB * NP + kTB * kCols + 2 * kTB;
+  constexpr int stage = 2 * kTB * NP + kTB * COLS + 2 * kTB;
   const int* si = seq_info + 4 * blockIdx.z;
   const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
   const int h = blockIdx.y, g = h / (H / G);
-  const int lc = threadIdx.x / kLPC, l = threadIdx.x % kLPC;
-  const int col = blockIdx.x * kCols + lc;
+  const int lc = threadIdx.x / LPC, l = threadIdx.x % LPC;
+  const int col = blockIdx.x * COLS + lc;
   const bool live = col < dv;
   for (int i = threadIdx.x; i < 2 * stage; i += blockDim.x) sm[i] = 0.f;      // the padding stays zero
   float* sp = state + (((long long)slot * H + h) * dv + (live ? col : 0)) * n;
   const bool n4 = (n & 3) == 0;
-  float S[R];
+  const bool wide_copy = n4 && (ldkq & 3) == 0 && ((reinterpret_cast<uintptr_t>(kvec) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(qvec) & 15) == 0);
+  float2 S[R / 2];
 #pragma unroll
   for (int r4 = 0; r4 < R4; ++r4) {
-    const int i = (r4 * kLPC + l) * 4;
+    const int i = (r4 * LPC + l) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live && seen > 0) {
       if (n4 && i < n) {
@@ -632,7 +673,7 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
         if (i + 3 < n) v.w = sp[i + 3];
       }
     }
-    S[4 * r4] = v.x, S[4 * r4 + 1] = v.y, S[4 * r4 + 2] = v.z, S[4 * r4 + 3] = v.w;
+    S[2 * r4] = make_float2(v.x, v.y), S[2 * r4 + 1] = make_float2(v.z, v.w);
   }
   const float D = skip ? skip[h] : 0.f;
   __syncthreads();
@@ -641,18 +682,28 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     float* sk = sm + buf * stage;
     float* sq = sk + kTB * NP;
     float* sv = sq + kTB * NP;
-    float* sa = sv + kTB * kCols;
+    float* sa = sv + kTB * COLS;
     float* sb = sa + kTB;
     const int nt = min(kTB, rows - t0);
-    for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
-      const int tt = i / n, c = i % n;
-      const long long row = first + t0 + tt;
-      __pipeline_memcpy_async(sk + tt * NP + c, kvec + row * ldkq + g * n + c, 4);
-      __pipeline_memcpy_async(sq + tt * NP + c, qvec + row * ldkq + g * n + c, 4);
+    if (wide_copy) {
+      const int nq4 = n >> 2;
+      for (int i = threadIdx.x; i < nt * nq4; i += blockDim.x) {
+        const int tt = i / nq4, c = (i % nq4) * 4;
+        const long long row = first + t0 + tt;
+        __pipeline_memcpy_async(sk + tt * NP + c, kvec + row * ldkq + g * n + c, 16);
+        __pipeline_memcpy_async(sq + tt * NP + c, qvec + row * ldkq + g * n + c, 16);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
+        const int tt = i / n, c = i % n;
+        const long long row = first + t0 + tt;
+        __pipeline_memcpy_async(sk + tt * NP + c, kvec + row * ldkq + g * n + c, 4);
+        __pipeline_memcpy_async(sq + tt * NP + c, qvec + row * ldkq + g * n + c, 4);
+      }
     }
-    for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
-      const int c = min((int)blockIdx.x * kCols + i % kCols, dv - 1);
-      __pipeline_memcpy_async(sv + i, val + (long long)(first + t0 + i / kCols) * ldv + h * dv + c, 4);
+    for (int i = threadIdx.x; i < nt * COLS; i += blockDim.x) {
+      const int c = min((int)blockIdx.x * COLS + i % COLS, dv - 1);
+      __pipeline_memcpy_async(sv + i, val + (long long)(first + t0 + i / COLS) * ldv + h * dv + c, 4);
     }
     for (int i = threadIdx.x; i < nt; i += blockDim.x) {
       __pipeline_memcpy_async(sa + i, decay + (long long)(first + t0 + i) * H + h, 4);
@@ -673,57 +724,65 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     const float* sk = sm + buf * stage;
     const float* sq = sk + kTB * NP;
     const float* sv = sq + kTB * NP;
-    const float* sa = sv + kTB * kCols;
+    const float* sa = sv + kTB * COLS;
     const float* sb = sa + kTB;
-    for (int tt = 0; tt < nt; ++tt) {
-      const float a = sa[tt], b = sb[tt], v = sv[tt * kCols + lc];
+    // One token.  A full group of TB tokens is walked by straight-line code, so the loads of k and q and the read-out
+    // reductions of neighbouring tokens overlap the serial part (the state update, and the dot product before it for
+    // the delta rule).
+    auto step = [&](int tt) {
+      const float a = sa[tt], b = sb[tt], v = sv[tt * COLS + lc];
       const float4* kk = reinterpret_cast<const float4*>(sk + tt * NP) + l;
       const float4* qq = reinterpret_cast<const float4*>(sq + tt * NP) + l;
       float4 k4[R4];
 #pragma unroll
-      for (int r4 = 0; r4 < R4; ++r4) k4[r4] = kk[r4 * kLPC];
+      for (int r4 = 0; r4 < R4; ++r4) k4[r4] = kk[r4 * LPC];
       float u = b * v;
-      if (delta) {                     // (a S)^T k = a (S^T k): the decay is folded into the update below
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      if (DELTA) {                     // (a S)^T k = a (S^T k): the decay is folded into the update below
+        float2 d01 = make_float2(0.f, 0.f), d23 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int r4 = 0; r4 < R4; ++r4) {
-          d0 += S[4 * r4] * k4[r4].x, d1 += S[4 * r4 + 1] * k4[r4].y;
-          d2 += S[4 * r4 + 2] * k4[r4].z, d3 += S[4 * r4 + 3] * k4[r4].w;
+          d01 = __ffma2_rn(S[2 * r4], make_float2(k4[r4].x, k4[r4].y), d01);
+          d23 = __ffma2_rn(S[2 * r4 + 1], make_float2(k4[r4].z, k4[r4].w), d23);
         }
-        float dot = (d0 + d1) + (d2 + d3);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        float dot = (d01.x + d01.y) + (d23.x + d23.y);
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         u = b * (v - a * dot);
       }
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      const float2 a2 = make_float2(a, a), u2 = make_float2(u, u);
+      float2 o01 = make_float2(0.f, 0.f), o23 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int r4 = 0; r4 < R4; ++r4) {
-        const float4 q4 = qq[r4 * kLPC];
-        S[4 * r4] = fmaf(k4[r4].x, u, S[4 * r4] * a), o0 += S[4 * r4] * q4.x;
-        S[4 * r4 + 1] = fmaf(k4[r4].y, u, S[4 * r4 + 1] * a), o1 += S[4 * r4 + 1] * q4.y;
-        S[4 * r4 + 2] = fmaf(k4[r4].z, u, S[4 * r4 + 2] * a), o2 += S[4 * r4 + 2] * q4.z;
-        S[4 * r4 + 3] = fmaf(k4[r4].w, u, S[4 * r4 + 3] * a), o3 += S[4 * r4 + 3] * q4.w;
+        const float4 q4 = qq[r4 * LPC];
+        S[2 * r4] = __ffma2_rn(make_float2(k4[r4].x, k4[r4].y), u2, __fmul2_rn(S[2 * r4], a2));
+        S[2 * r4 + 1] = __ffma2_rn(make_float2(k4[r4].z, k4[r4].w), u2, __fmul2_rn(S[2 * r4 + 1], a2));
+        o01 = __ffma2_rn(S[2 * r4], make_float2(q4.x, q4.y), o01);
+        o23 = __ffma2_rn(S[2 * r4 + 1], make_float2(q4.z, q4.w), o23);
       }
-      float o = (o0 + o1) + (o2 + o3);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      float o = (o01.x + o01.y) + (o23.x + o23.y);
+#pragma unroll
+      for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
       if (live && l == 0) out[(long long)(first + t0 + tt) * H * dv + h * dv + col] = o + D * v;
+    };
+    if (nt == kTB) {
+#pragma unroll
+      for (int tt = 0; tt < kTB; ++tt) step(tt);
+    } else {
+      for (int tt = 0; tt < nt; ++tt) step(tt);
     }
     __syncthreads();          // the buffer just walked is the target of the next iteration's copies
   }
   if (live) {
 #pragma unroll
     for (int r4 = 0; r4 < R4; ++r4) {
-      const int i = (r4 * kLPC + l) * 4;
+      const int i = (r4 * LPC + l) * 4;
       if (n4 && i < n) {
-        *reinterpret_cast<float4*>(sp + i) = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]);
+        *reinterpret_cast<float4*>(sp + i) = make_float4(S[2 * r4].x, S[2 * r4].y, S[2 * r4 + 1].x, S[2 * r4 + 1].y);
       } else {
-        if (i < n) sp[i] = S[4 * r4];
-        if (i + 1 < n) sp[i + 1] = S[4 * r4 + 1];
-        if (i + 2 < n) sp[i + 2] = S[4 * r4 + 2];
-        if (i + 3 < n) sp[i + 3] = S[4 * r4 + 3];
+        if (i < n) sp[i] = S[2 * r4].x;
+        if (i + 1 < n) sp[i + 1] = S[2 * r4].y;
+        if (i + 2 < n) sp[i + 2] = S[2 * r4 + 1].x;
+        if (i + 3 < n) sp[i + 3] = S[2 * r4 + 1].y;
       }
     }
   }
@@ -845,7 +904,7 @@ template <typename T, int NV>
 static int launch_attention_tiles(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                   const void* atoms, int n_long, const void* tables, int max_blocks, int block_size,
                                   int Hq, int G, int d, int dv, float scale, int chunk, cudaStream_t s) {
-  const size_t smem = (size_t)(2 * kBQ * (d + 4) + kBK * NV * 64 + kBQ * (kBK + 4)) * sizeof(float);
+  const size_t smem = (size_t)(kBQ * (d + 4) + std::max(kBK * (d + 4), kBQ * (kBK + 4)) + kBK * NV * 64) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sink_attention_tile_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -953,18 +1012,22 @@ SXB_API int sxb_linear_recurrence(const void* kvec, const void* qvec, long long 
                                   void* stream) {
   if (n_seqs <= 0) return SXB_OK;
   if (n > 256 || H % G) return SXB_ERR_UNSUPPORTED;
-  dim3 grid((dv + kCols - 1) / kCols, H, n_seqs);
-  const int np = n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256));
-  const size_t smem = (size_t)2 * (2 * kTB * np + kTB * kCols + 2 * kTB) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
-#define LAUNCH_REC(R)                                                                                              \
-  linear_recurrence_kernel<R><<<grid, kLPC * kCols, smem, s>>>(                                                     \
-      (const float*)kvec, (const float*)qvec, ldkq, (const float*)val, ldv, (const float*)decay, (const float*)beta, \
-      (const float*)skip, (float*)state, (float*)out, (const int*)seq_info, H, G, n, dv, delta)
-  if (n <= 32) LAUNCH_REC(4);
-  else if (n <= 64) LAUNCH_REC(8);
-  else if (n <= 128) LAUNCH_REC(16);
-  else LAUNCH_REC(32);
+#define LAUNCH_REC(R, D, LPC)                                                                                       \
+  do {                                                                                                              \
+    constexpr int cols = kRecThreads / LPC;                                                                         \
+    const size_t smem = (size_t)2 * (2 * kTB * (R * LPC) + kTB * cols + 2 * kTB) * sizeof(float);                   \
+    linear_recurrence_kernel<R, D, LPC><<<dim3((dv + cols - 1) / cols, H, n_seqs), kRecThreads, smem, s>>>(         \
+        (const float*)kvec, (const float*)qvec, ldkq, (const float*)val, ldv, (const float*)decay,                  \
+        (const float*)beta, (const float*)skip, (float*)state, (float*)out, (const int*)seq_info, H, G, n, dv);     \
+  } while (0)
+#define LAUNCH_REC_N(D)                                  \
+  if (n <= 32) LAUNCH_REC(4, D, 8);                      \
+  else if (n <= 64) LAUNCH_REC(8, D, 8);                 \
+  else if (n <= 128) LAUNCH_REC(16, D, 8);               \
+  else LAUNCH_REC(32, D, 8)
+  if (delta) { LAUNCH_REC_N(true); } else { LAUNCH_REC_N(false); }
+#undef LAUNCH_REC_N
 #undef LAUNCH_REC
   SXB_CHECK_LAUNCH();
   return SXB_OK;

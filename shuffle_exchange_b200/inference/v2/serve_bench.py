@@ -25,7 +25,7 @@ SIZES = {
     "w4096": dict(width=4096, layers=3, heads=32, kv_heads=8, head=128, ff=14336, ssd_heads=64, ssd_vdim=128, state=128),
 }
 VOCAB = 32000
-CHUNK = 1024
+CHUNK = 4096          # the prompt and the decode context fall into one chunk: attention work equals full causal
 
 
 def hybrid_config(z: Dict) -> Dict:
@@ -151,7 +151,8 @@ def engine_throughput(build, z: Dict, prefill: int, batch: int, context: int, st
             "decode_tok_s": round(batch / ms_d * 1e3)}
 
 
-def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs: float) -> List[Dict]:
+def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs: float,
+                 peak_tflops: Dict[str, float]) -> List[Dict]:
     """Device time, algorithmic bytes and fraction of the copy bandwidth for the hybrid stack's kernels and the Llama
     kernels that do the like job, at prefill (one request) and decode (``batch`` requests) shapes."""
     from ...ops import functional as F
@@ -163,10 +164,16 @@ def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs
     Hs, dvs, N = z["ssd_heads"], z["ssd_vdim"], z["state"]
     rows: List[Dict] = []
 
-    def add(name, phase, fn, nbytes, flops=0.0):
+    def add(name, phase, fn, nbytes, flops=0.0, pipe=None):
+        """``pipe``: the arithmetic unit the kernel's products run on ("fp32": FMA lanes, "bf16": tensor cores); the
+        roofline time is the larger of bytes / copy bandwidth and FLOPs / that unit's peak."""
         ms = timer(fn, 5, 3)
+        ideal_ms = nbytes / hbm_gbs / 1e6
+        if pipe is not None:
+            ideal_ms = max(ideal_ms, flops / peak_tflops[pipe] / 1e9)
         rows.append({"kernel": name, "phase": phase, "ms": round(ms, 4), "GB_s": round(nbytes / ms / 1e6, 1),
-                     "of_measured_hbm": round(nbytes / ms / 1e6 / hbm_gbs, 3), "GFLOP_s": round(flops / ms / 1e6, 1)})
+                     "of_measured_hbm": round(nbytes / ms / 1e6 / hbm_gbs, 3), "GFLOP_s": round(flops / ms / 1e6, 1),
+                     "pipe": pipe or "memory", "of_roofline": round(ideal_ms / ms, 3)})
 
     for phase, T, n_seq, seen in (("prefill", prefill, 1, 0), ("decode", batch, batch, context)):
         per = T // n_seq
@@ -214,11 +221,11 @@ def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs
         atoms, n_long = wrap.atoms(), wrap.atoms_longer_than(M.SHORT_ATOM)
         add(f"sink_attention (chunk {CHUNK}, fp32 weights)", phase,
             lambda: M.sink_attention(q32, kc, vc, sink, t2s, pos, tables, d ** -0.5, CHUNK, bf, atoms, n_long),
-            kv_bytes + T * H * d * 6, fl)
+            kv_bytes + T * H * d * 6, fl, "fp32")
         qv = qkv.view(T, H + 2 * G, d)[:, :H]
         full_keys = (per + 1) / 2 if phase == "prefill" else tot
         add("llama ragged_attention (full causal)", phase, lambda: R.ragged_attention(qv, cache, wrap),
-            n_seq * tot * 2 * G * d * 2 + T * H * d * 4, 4.0 * T * H * d * full_keys)
+            n_seq * tot * 2 * G * d * 2 + T * H * d * 4, 4.0 * T * H * d * full_keys, "bf16")
         # recurrences
         for name, Hh, Gg, n, dv, delta in (("delta", H, H, d, d, True), ("ssd", Hs, 1, N, dvs, False)):
             C = (2 * Gg * n + Hh * dv)
@@ -236,7 +243,7 @@ def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs
             add(f"linear_recurrence ({name})", phase,
                 lambda: M.linear_recurrence(xc[:, : Gg * n], xc[:, Gg * n: 2 * Gg * n], xc[:, 2 * Gg * n:], decay, beta,
                                             None, S, info, Hh, Gg, n, dv, delta),
-                state_bytes + T * (C * 4 + Hh * dv * 4), (6.0 if delta else 4.0) * T * Hh * dv * n)
+                state_bytes + T * (C * 4 + Hh * dv * 4), (6.0 if delta else 4.0) * T * Hh * dv * n, "fp32")
             o = torch.randn(T, Hh * dv, device=dev)
             gate = torch.randn(T, Hh * dv, device=dev).to(bf)
             nw = torch.ones(dv if delta else Hh * dv, device=dev, dtype=bf)
@@ -246,17 +253,26 @@ def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs
     return rows
 
 
-def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, warmup: int, kernels: bool = True) -> Dict:
+def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, warmup: int, kernels: bool = True,
+        chunk: int = 0) -> Dict:
+    global CHUNK
+    if chunk > 0:
+        CHUNK = chunk
     peaks = {}
     p = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "MEASURED_PEAKS.json")
     if os.path.isfile(p):
         with open(p) as f:
             peaks = json.load(f)
     hbm = float(peaks.get("hbm_gbs", 6650.0))
+    sm_mhz = float(peaks.get("sm_max_mhz", 1965.0))
+    # fp32 FMA lanes: 148 SMs x 128 lanes x 2 FLOPs per clock at the maximum SM clock; tensor cores: the measured GEMM
+    peak_tflops = {"fp32": 148 * 128 * 2 * sm_mhz * 1e6 / 1e12, "bf16": float(peaks.get("bf16_tflops", 1590.0))}
     timer = _Timer()
     out = {"metric": "serving tokens/s, hybrid (Fomalix) vs Llama stack of equal size", "dtype": "bf16",
            "data": "synthetic", "weights": "random", "hbm_gbs_denominator": hbm,
            "denominator_source": "measured" if peaks else "fallback", "l2": "256 MB buffer rewritten between forwards",
+           "attention_chunk": CHUNK, "fp32_fma_tflops_nominal": round(peak_tflops["fp32"], 1),
+           "bf16_tflops_denominator": peak_tflops["bf16"],
            "sizes": {}}
     for name in sizes:
         z = SIZES[name]
@@ -264,6 +280,6 @@ def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, wa
                  "fomalix": engine_throughput(build_hybrid, z, prefill, batch, context, steps, warmup, timer),
                  "llama": engine_throughput(build_llama, z, prefill, batch, context, steps, warmup, timer)}
         if kernels:
-            entry["kernels"] = kernel_table(z, prefill, batch, context, timer, hbm)
+            entry["kernels"] = kernel_table(z, prefill, batch, context, timer, hbm, peak_tflops)
         out["sizes"][name] = entry
     return out

@@ -196,6 +196,36 @@ def test_recurrence_op_matches_its_equations_and_ignores_a_used_slot():
         assert torch.all(state[0] == 3.0)
 
 
+@pytest.mark.parametrize("n,dv,portions", [(128, 24, (19, 18)), (130, 20, (37,)), (64, 17, (8, 16, 9)), (40, 33, (33,))])
+def test_recurrence_op_over_many_rows_and_wide_states(n, dv, portions):
+    """Rows beyond one staging group of the kernel, state sizes on both sides of its register layouts' limits."""
+    g = torch.Generator().manual_seed(n + dv)
+    T, H, G = sum(portions), 3, 1
+    kv = torch.randn(T, G * n, generator=g) / n ** 0.5
+    qv = torch.randn(T, G * n, generator=g) / n ** 0.5
+    val = torch.randn(T, H * dv, generator=g)
+    decay, beta = torch.rand(T, H, generator=g) * 0.2 + 0.8, torch.rand(T, H, generator=g)
+    for delta in (True, False):
+        want = torch.zeros(T, H, dv, dtype=torch.float64)
+        for h in range(H):
+            S = torch.zeros(n, dv, dtype=torch.float64)
+            for t in range(T):
+                S = decay[t, h].double() * S
+                v = val.view(T, H, dv)[t, h].double()
+                u = beta[t, h].double() * ((v - S.T @ kv[t].double()) if delta else v)
+                S = S + torch.outer(kv[t].double(), u)
+                want[t, h] = S.T @ qv[t].double()
+        state = torch.full((1, H, dv, n), -2.0, device=DEV)
+        got, lo = [], 0
+        for rows in portions:
+            info = torch.tensor([[0, rows, lo, 0]], dtype=torch.int32, device=DEV)
+            sl = slice(lo, lo + rows)
+            got.append(M.linear_recurrence(kv[sl].to(DEV), qv[sl].to(DEV), val[sl].to(DEV), decay[sl].to(DEV),
+                                           beta[sl].to(DEV), None, state, info, H, G, n, dv, delta).cpu())
+            lo += rows
+        assert torch.allclose(torch.cat(got).double().view(T, H, dv), want, atol=2e-4)
+
+
 def test_far_token_reaches_the_end_through_the_recurrent_state():
     """A delta-rule layer with decay ~1 keeps what an early token wrote: changing token 2 of a long prompt must change
     the last logits by the amount the plain evaluation says, after decoding through many steps."""
