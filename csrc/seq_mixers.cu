@@ -729,13 +729,22 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     // One token.  A full group of TB tokens is walked by straight-line code, so the loads of k and q and the read-out
     // reductions of neighbouring tokens overlap the serial part (the state update, and the dot product before it for
     // the delta rule).
-    auto step = [&](int tt) {
-      const float a = sa[tt], b = sb[tt], v = sv[tt * COLS + lc];
+    struct Tok {                      // one token's operands, loaded one token ahead of their use
+      float a, b, v;
+      float4 k[R4], q[R4];
+    };
+    auto fetch = [&](int tt) {
+      Tok t;
+      t.a = sa[tt], t.b = sb[tt], t.v = sv[tt * COLS + lc];
       const float4* kk = reinterpret_cast<const float4*>(sk + tt * NP) + l;
       const float4* qq = reinterpret_cast<const float4*>(sq + tt * NP) + l;
-      float4 k4[R4];
 #pragma unroll
-      for (int r4 = 0; r4 < R4; ++r4) k4[r4] = kk[r4 * LPC];
+      for (int r4 = 0; r4 < R4; ++r4) t.k[r4] = kk[r4 * LPC], t.q[r4] = qq[r4 * LPC];
+      return t;
+    };
+    auto step = [&](const Tok& t, float& o_lane) {
+      const float a = t.a, b = t.b, v = t.v;
+      const float4* k4 = t.k;
       float u = b * v;
       if (DELTA) {                     // (a S)^T k = a (S^T k): the decay is folded into the update below
         float2 d01 = make_float2(0.f, 0.f), d23 = make_float2(0.f, 0.f);
@@ -753,22 +762,42 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
       float2 o01 = make_float2(0.f, 0.f), o23 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int r4 = 0; r4 < R4; ++r4) {
-        const float4 q4 = qq[r4 * LPC];
+        const float4 q4 = t.q[r4];
         S[2 * r4] = __ffma2_rn(make_float2(k4[r4].x, k4[r4].y), u2, __fmul2_rn(S[2 * r4], a2));
         S[2 * r4 + 1] = __ffma2_rn(make_float2(k4[r4].z, k4[r4].w), u2, __fmul2_rn(S[2 * r4 + 1], a2));
         o01 = __ffma2_rn(S[2 * r4], make_float2(q4.x, q4.y), o01);
         o23 = __ffma2_rn(S[2 * r4 + 1], make_float2(q4.z, q4.w), o23);
       }
-      float o = (o01.x + o01.y) + (o23.x + o23.y);
-#pragma unroll
-      for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
-      if (live && l == 0) out[(long long)(first + t0 + tt) * H * dv + h * dv + col] = o + D * v;
+      o_lane = (o01.x + o01.y) + (o23.x + o23.y);       // this lane's part of the read-out
     };
     if (nt == kTB) {
+      // the read-outs of the group are summed over the column's lanes together, off the serial path: TB independent
+      // shuffle trees, then lane t of the column writes token t
+      static_assert(LPC == kTB, "lane t of a column writes token t of the group");
+      float op[kTB];
+      Tok cur = fetch(0);
 #pragma unroll
-      for (int tt = 0; tt < kTB; ++tt) step(tt);
+      for (int tt = 0; tt < kTB; ++tt) {
+        const Tok nxt = fetch(tt + 1 < kTB ? tt + 1 : tt);
+        step(cur, op[tt]);
+        cur = nxt;
+      }
+#pragma unroll
+      for (int x = 1; x < LPC; x <<= 1)
+#pragma unroll
+        for (int tt = 0; tt < kTB; ++tt) op[tt] += __shfl_xor_sync(0xffffffffu, op[tt], x);
+      float mine = op[0];
+#pragma unroll
+      for (int tt = 1; tt < kTB; ++tt) mine = (l == tt) ? op[tt] : mine;
+      if (live) out[(long long)(first + t0 + l) * H * dv + h * dv + col] = mine + D * sv[l * COLS + lc];
     } else {
-      for (int tt = 0; tt < nt; ++tt) step(tt);
+      for (int tt = 0; tt < nt; ++tt) {
+        float o;
+        step(fetch(tt), o);
+#pragma unroll
+        for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+        if (live && l == 0) out[(long long)(first + t0 + tt) * H * dv + h * dv + col] = o + D * sv[tt * COLS + lc];
+      }
     }
     __syncthreads();          // the buffer just walked is the target of the next iteration's copies
   }

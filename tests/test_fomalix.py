@@ -79,6 +79,22 @@ def test_one_layer_of_each_kind(layer):
     close(feed(eng, 1, toks, [len(toks)]), want)
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(6, 2, 12, 8), (8, 2, 16, 20), (8, 1, 8, 136), (5, 5, 24, 132)],
+                         ids=["group_of_3", "group_of_4", "group_of_8_wide_values", "no_sharing_wide_values"])
+def test_attention_head_groupings(heads, kv_heads, dim, vdim):
+    """Every way the kernels take the query heads of a key/value head together, and value heads on both sides of 128;
+    a whole prompt, portions that start inside a chunk, and single tokens."""
+    layer = dict(ATTN, mixer={"dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": 21}, "scale": dim ** -0.5,
+                              "vdim": vdim})
+    cfg = make_cfg([layer], width=40)
+    W = O.random_weights(cfg, seed=heads)
+    toks = tokens(50, cfg["vocab"], 3)
+    want, _ = O.forward(toks, W, cfg)
+    eng = make_engine(cfg, W, block_size=8)
+    close(feed(eng, 1, toks, [len(toks)]), want)
+    close(feed(eng, 2, toks, [19, 17, 5] + [1] * 9), want)
+
+
 def test_short_conv_carries_inputs_across_calls():
     g = torch.Generator().manual_seed(3)
     C, taps, T = 10, 4, 9
