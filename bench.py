@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 N > 1 is launched by the driver as ``python -m torch.distributed.run --nproc-per-node N ... bench.py
---gpus N`` (one rank per GPU, NCCL).  Prints ONE JSON line on rank 0 (contract in the task brief).
+--gpus N`` (one rank per GPU, NCCL).  Prints ONE JSON line on rank 0.
 
 Timed region = K full training steps (forward + backward with activation recomputation + ZeRO-3
 gradient reduction + AdamW update on fp32 master shards), bracketed by barrier + synchronize, CUDA
