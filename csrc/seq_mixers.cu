@@ -576,6 +576,80 @@ conv_silu_kernel(const T* __restrict__ x, long long ld, const T* __restrict__ w,
   }
 }
 
+// The same filter for channel counts and row pitches that are multiples of 8: a thread takes 8 channels (16-byte loads
+// of bf16, two of fp32) and walks kConvRows consecutive batch rows with the last TAPS-1 inputs in registers.  The window
+// is loaded by the rule above at the thread's first row and at a sequence's first row in the batch, and shifted
+// otherwise; the sum runs in the same order as in the scalar kernel.
+constexpr int kConvRows = 8;
+
+template <typename T>
+__device__ __forceinline__ void load8_f32(const T* p, float* o);
+template <>
+__device__ __forceinline__ void load8_f32<float>(const float* p, float* o) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8_f32<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[2 * i] = __low2float(h[i]), o[2 * i + 1] = __high2float(h[i]);
+}
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128)
+conv_silu_vec_kernel(const T* __restrict__ x, long long ld, const T* __restrict__ w, const T* __restrict__ bias,
+                     const T* __restrict__ state, const int* __restrict__ seq_info, const int* __restrict__ tok_seq,
+                     float* __restrict__ out, int C, int n_tokens) {
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int t0 = blockIdx.x * kConvRows, t1 = min(t0 + kConvRows, n_tokens);
+  float wt[8][TAPS], b8[8], hist[TAPS][8];      // hist[j]: the input j rows back (hist[0]: the current row)
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    b8[e] = bias ? to_f32<T>(bias[c0 + e]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[e][j] = to_f32<T>(w[(long long)(c0 + e) * TAPS + j]);
+  }
+  for (int t = t0; t < t1; ++t) {
+    const int* si = seq_info + 4 * tok_seq[t];
+    const int local = t - si[0], seen = si[2];
+    if (t == t0 || local == 0) {
+      const T* st = state + (long long)si[3] * (TAPS - 1) * C;
+#pragma unroll
+      for (int j = 1; j < TAPS; ++j) {
+        const int src = local - j;
+        if (src >= 0) {
+          load8_f32<T>(x + (long long)(t - j) * ld + c0, hist[j]);
+        } else if (seen + src >= 0) {
+          load8_f32<T>(st + (long long)(TAPS - 1 + src) * C + c0, hist[j]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) hist[j][e] = 0.f;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = TAPS - 1; j >= 1; --j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) hist[j][e] = hist[j - 1][e];
+    }
+    load8_f32<T>(x + (long long)t * ld + c0, hist[0]);
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float a = b8[e];
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) a += wt[e][TAPS - 1 - j] * hist[j][e];
+      o[e] = silu_f(a);
+    }
+    float4* op = reinterpret_cast<float4*>(out + (long long)t * C + c0);
+    op[0] = make_float4(o[0], o[1], o[2], o[3]);
+    op[1] = make_float4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 // After conv_silu of a batch: each slot keeps the last taps-1 inputs of (carried inputs ++ this batch's rows).
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -985,6 +1059,22 @@ SXB_API int sxb_conv_silu(const void* x, long long ld, const void* w, const void
                           int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
   if (taps < 1 || taps > kMaxTaps) return SXB_ERR_UNSUPPORTED;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(state) |
+                         reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  // few rows (decode batches): the one-thread-per-element kernel spreads them over more CTAs
+  if (n_tokens >= 128 && taps >= 2 && taps <= 4 && C % 8 == 0 && ld % 8 == 0 && aligned) {
+    dim3 vgrid((n_tokens + kConvRows - 1) / kConvRows, (C / 8 + 127) / 128);
+#define CONV_VEC(TAPS)                                                                                             \
+  SEQMIX_DISPATCH(dtype, (conv_silu_vec_kernel<T, TAPS><<<vgrid, 128, 0, (cudaStream_t)stream>>>(                  \
+                             (const T*)x, ld, (const T*)w, (const T*)bias, (const T*)state, (const int*)seq_info,  \
+                             (const int*)tok_seq, (float*)out, C, n_tokens)))
+    if (taps == 2) CONV_VEC(2);
+    else if (taps == 3) CONV_VEC(3);
+    else CONV_VEC(4);
+#undef CONV_VEC
+    SXB_CHECK_LAUNCH();
+    return SXB_OK;
+  }
   dim3 grid(n_tokens, (C + 1023) / 1024);
   SEQMIX_DISPATCH(dtype, (conv_silu_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
                              (const T*)x, ld, (const T*)w, (const T*)bias, (const T*)state, (const int*)seq_info,

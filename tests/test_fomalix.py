@@ -114,6 +114,42 @@ def test_short_conv_carries_inputs_across_calls():
     assert torch.all(state[:2] == 7.0)
 
 
+@pytest.mark.parametrize("taps", [2, 3, 4, 5])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_short_conv_over_channel_groups_of_8_and_several_sequences(taps, dtype):
+    """Channel counts and pitches that are multiples of 8 (16-byte loads), three sequences of unequal portions in each
+    batch, portions longer than the kernel's row groups, the input a column slice of a wider matrix."""
+    g = torch.Generator().manual_seed(taps)
+    C, lens = 24, (229, 3, 11)
+    xs = [torch.randn(n, C, generator=g).to(dtype) for n in lens]
+    w, b = torch.randn(C, taps, generator=g).to(dtype), torch.randn(C, generator=g).to(dtype)
+    want = [O.silu(O.short_conv(x.double(), w.double(), b.double())) for x in xs]
+    state = torch.full((4, taps - 1, C), -5.0, device=DEV, dtype=dtype)
+    cuts = ([17, 201, 11], [2, 1], [1, 9, 1])                       # per sequence; batch i holds every i-th portion
+    at, got = [0, 0, 0], [[], [], []]
+    for i in range(3):
+        rows, info, t2s = [], [], []
+        for q in range(3):
+            if i >= len(cuts[q]):
+                continue
+            n = cuts[q][i]
+            info.append([sum(r.shape[0] for r in rows), n, at[q], q + 1])
+            t2s += [len(info) - 1] * n
+            rows.append(xs[q][at[q]: at[q] + n])
+            at[q] += n
+        wide = torch.zeros(len(t2s), 8 + C + 8, dtype=dtype)
+        wide[:, 8: 8 + C] = torch.cat(rows)
+        xin = wide.to(DEV)[:, 8: 8 + C]
+        info_t = torch.tensor(info, dtype=torch.int32, device=DEV)
+        out = M.conv_silu(xin, w.to(DEV), b.to(DEV), state, info_t, torch.tensor(t2s, dtype=torch.int32, device=DEV)).cpu()
+        M.conv_state_update(xin, state, info_t)
+        for k, row in enumerate(info):
+            got[row[3] - 1].append(out[row[0]: row[0] + row[1]])
+    for q in range(3):
+        assert torch.allclose(torch.cat(got[q]).double(), want[q], atol=1e-5)
+    assert torch.all(state[0] == -5.0)
+
+
 def _attend(q, k, v, sink, scale, chunk, block_size, pos0=0):
     """Run the attention op for queries at positions pos0.. over keys 0.. laid out in shuffled pages."""
     Tk, G, d = k.shape
