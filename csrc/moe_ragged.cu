@@ -25,6 +25,8 @@ constexpr int kMaxTopK = 8;
 // One warp per token.  logits [T, E] (any float dtype) -> softmax over ALL experts (fp32), top-k by repeated
 // warp arg-max, scores [T, K] (fp32, optionally renormalised over the k winners), assignments [T, K] (int32),
 // offsets [T, K] = arrival order of the token inside its expert (atomicAdd on expert_counts [E]).
+// `renormalize` is a set of flags: bit 0 divides the k scores by their sum; bit 1 scores every expert on its own with
+// sigmoid(logit) instead of the softmax over all experts (the same experts win: both are increasing in the logit).
 template <typename T>
 __global__ void __launch_bounds__(256)
 top_k_gating_kernel(const T* __restrict__ logits, float* __restrict__ scores, int* __restrict__ assignments,
@@ -73,12 +75,12 @@ top_k_gating_kernel(const T* __restrict__ logits, float* __restrict__ scores, in
 #pragma unroll
     for (int i = 0; i < PER; ++i)
       if (i * 32 + lane == best_e) v[i] = -INFINITY;
-    my_score[k] = __expf(best - mx) * inv;
+    my_score[k] = (renormalize & 2) ? 1.f / (1.f + expf(-best)) : __expf(best - mx) * inv;
     my_expert[k] = best_e;
     picked_sum += my_score[k];
   }
   if (lane == 0) {
-    const float norm = renormalize ? 1.f / picked_sum : 1.f;
+    const float norm = (renormalize & 1) ? 1.f / picked_sum : 1.f;
     for (int k = 0; k < top_k; ++k) {
       const long long o = (long long)warp * top_k + k;
       scores[o] = my_score[k] * norm;
@@ -125,6 +127,30 @@ moe_scatter_kernel(const uint4* __restrict__ x, uint4* __restrict__ moe_input, c
   for (int i = threadIdx.x; i < row_vec; i += blockDim.x) {
     const uint4 v = src[i];
     for (int k = 0; k < top_k; ++k) moe_input[slot[k] * row_vec + i] = v;
+  }
+}
+
+// Scatter with the routing weight applied on the way in: moe_input[slot(t, k)] = x[t] * scores[t, k] (product in fp32,
+// rounded once), for layers whose experts see w * x instead of having their output scaled.  Any width, bf16 or fp32.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_scatter_scaled_kernel(const T* __restrict__ x, const float* __restrict__ scores, T* __restrict__ moe_input,
+                          const int* __restrict__ assignments, const int* __restrict__ offsets,
+                          const long long* __restrict__ cumsum, int* __restrict__ mapped_slots, int hidden, int top_k) {
+  const int t = blockIdx.x;
+  __shared__ long long slot[kMaxTopK];
+  __shared__ float wt[kMaxTopK];
+  if (threadIdx.x < top_k) {
+    const long long o = (long long)t * top_k + threadIdx.x;
+    const int e = assignments[o];
+    slot[threadIdx.x] = (e > 0 ? cumsum[e - 1] : 0) + offsets[o];
+    wt[threadIdx.x] = scores[o];
+    mapped_slots[o] = (int)slot[threadIdx.x];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = to_f32<T>(x[(long long)t * hidden + c]);
+    for (int k = 0; k < top_k; ++k) moe_input[slot[k] * hidden + c] = from_f32<T>(v * wt[k]);
   }
 }
 
@@ -416,6 +442,30 @@ SXB_API int sxb_moe_scatter(const void* x, void* moe_input, const void* assignme
                                                    static_cast<const int*>(assignments), static_cast<const int*>(offsets),
                                                    static_cast<const long long*>(expert_cumsum),
                                                    static_cast<int*>(mapped_slots), hidden * elem_size / 16, top_k);
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+// As sxb_moe_scatter with every copied row multiplied by its routing weight: moe_input[slot(t, k)] = x[t] * scores[t, k].
+// x / moe_input `dtype` (bf16 or fp32) of any width, scores fp32 [T, K].
+SXB_API int sxb_moe_scatter_scaled(const void* x, const void* scores, void* moe_input, const void* assignments,
+                                   const void* offsets, const void* expert_counts, void* expert_cumsum,
+                                   void* mapped_slots, int n_tokens, int n_experts, int top_k, int hidden, int dtype,
+                                   void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (n_experts > moe::kMaxExperts || top_k > moe::kMaxTopK) return SXB_ERR_UNSUPPORTED;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  moe::expert_cumsum_kernel<<<1, 1024, 0, s>>>(static_cast<const int*>(expert_counts),
+                                               static_cast<long long*>(expert_cumsum), n_experts);
+  const int *as = static_cast<const int*>(assignments), *of = static_cast<const int*>(offsets);
+  const long long* cs = static_cast<const long long*>(expert_cumsum);
+  const float* sc = static_cast<const float*>(scores);
+  int* ms = static_cast<int*>(mapped_slots);
+  switch (dtype) {
+    case kBF16: moe::moe_scatter_scaled_kernel<<<n_tokens, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x), sc, static_cast<__nv_bfloat16*>(moe_input), as, of, cs, ms, hidden, top_k); break;
+    case kF32: moe::moe_scatter_scaled_kernel<<<n_tokens, 128, 0, s>>>(static_cast<const float*>(x), sc, static_cast<float*>(moe_input), as, of, cs, ms, hidden, top_k); break;
+    default: return SXB_ERR_UNSUPPORTED;
+  }
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

@@ -6,15 +6,20 @@
 // sequence, `block_tables[s]` its pages of the key/value cache.  `T` is the activation type (bf16 when serving,
 // float for exact evaluation); everything that the recurrences, norms and softmax touch is fp32 in both.
 //
-//   embed_sinusoid        token row * scale + sinusoidal position vector            -> fp32 residual
+//   embed_sinusoid        token row * scale (+ sinusoidal position vector)          -> fp32 residual
 //   resid_norm_step       residual += rms(y) * w_post (+ extra);  out = rms(residual) * w_pre   (one pass per row)
 //   qk_norm_append        bias + per-head unit-RMS of q and k, q -> fp32, k / v -> paged cache
-//   sink_attention        causal or chunk-local softmax attention over the paged cache with a per-head sink logit
+//   sink_attention        causal, chunk-local or sliding-window softmax attention over the paged cache with a per-head
+//                         sink logit; values may be a column range of the key rows (attention in a latent space)
 //   conv_silu / conv_state_update   short causal per-channel filter with its carried inputs per state slot
 //   unit_norm_heads, recurrence_gates   per-head L2 normalisation; decay / write strength of the recurrences
 //   linear_recurrence     S <- a S;  u = b (v - [delta] S^T k);  S <- S + k u^T;  o = S^T q (+ D v), state per slot
 //   group_norm_gate       RMS norm over channel groups combined with a SiLU gate (before or after the norm)
-//   gated_act_rows        act(gate) * up for any width and fp32 or bf16 rows
+//   gated_act_rows, bias_act_rows   act(gate) * up, act(x + bias) for any width and fp32 or bf16 rows
+//   conv_residual, post_norm_mix, rms_scale_rows   post-norm layers: x + filter(x) in front of a sublayer,
+//                         x += scale (.) rms(y) * gain behind it (+ a weighted sum of all layers' streams), final norm
+//   rms_norm_slice, latent_qk_prepare   latent attention: query latent norm; key latent norm + rotation + cache append
+//   mlstm_prepare / mlstm_gate_scan / mlstm_output   matrix-memory LSTM around linear_recurrence
 #include <algorithm>
 #include "sxb_common.cuh"
 #include <cuda_pipeline.h>
@@ -54,7 +59,7 @@ embed_sinusoid_kernel(const int* __restrict__ ids, const int* __restrict__ pos, 
     const int i = c >> 1;
     const float freq = exp2f(-(2.f * (float)i / (float)width) * lb);
     const float ang = p * freq;
-    const float pe = (c & 1) ? cosf(ang) : sinf(ang);
+    const float pe = base > 0.f ? ((c & 1) ? cosf(ang) : sinf(ang)) : 0.f;      // base <= 0: no position vector
     out[(long long)t * width + c] = to_f32<T>(row[c]) * scale + pe;
   }
 }
@@ -133,6 +138,13 @@ qk_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restri
   }
 }
 
+// First position a query at `pos` attends to: the start of its aligned chunk (chunk > 0), else the start of a sliding
+// window of `window` positions that ends at the query (window > 0), else the start of the sequence.
+__device__ __forceinline__ int first_key(int pos, int chunk, int window) {
+  if (chunk > 0) return (pos / chunk) * chunk;
+  return window > 0 ? max(0, pos - window + 1) : 0;
+}
+
 constexpr int kMaxVPerLane = 8;      // value head size <= 256
 constexpr int kShortAtom = 16;       // atoms of at most this many queries run one warp per (query, head)
 constexpr int kBQ = 64, kBK = 64;    // query rows / keys per tile of the tiled kernel
@@ -161,7 +173,7 @@ __global__ void __launch_bounds__(256, NV <= 2 ? 2 : 1)
 sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                            const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ atoms,
                            const int* __restrict__ tables, int max_blocks, int block_size, int Hq, int G, int d,
-                           int dv, float scale, int chunk) {
+                           int dv, float scale, int chunk, int window, int kpitch, int vpitch) {
   extern __shared__ __align__(16) float smf[];
   const int dp = d + 4, vp = NV * 64, pp = kBK + 4;
   float* Qs = smf;
@@ -196,7 +208,7 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
     for (int c = 0; c < NV * 2; ++c) acc[i][c] = make_float2(0.f, 0.f);
   }
   const int last = pos0 + nq - 1;
-  const int kbeg = chunk > 0 ? (pos0 / chunk) * chunk : 0;
+  const int kbeg = first_key(pos0, chunk, window);
   for (int k0 = kbeg; k0 <= last; k0 += kBK) {
     __syncthreads();
     for (int i = tid; i < kBK * d4; i += 256) {
@@ -204,7 +216,7 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (kj <= last) {
         const long long slot = (long long)tab[kj / block_size] * block_size + kj % block_size;
-        v = load4_f32<T>(kcache + (slot * G + g) * d + c);
+        v = load4_f32<T>(kcache + slot * kpitch + g * d + c);
       }
       *reinterpret_cast<float4*>(Ks + r * dp + c) = v;
     }
@@ -213,7 +225,7 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (kj <= last && c < dv) {
         const long long slot = (long long)tab[kj / block_size] * block_size + kj % block_size;
-        v = load4_f32<T>(vcache + (slot * G + g) * dv + c);
+        v = load4_f32<T>(vcache + slot * vpitch + g * dv + c);
       }
       *reinterpret_cast<float4*>(Vs + r * vp + c) = v;
     }
@@ -246,7 +258,7 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = ty + 16 * i, qp = pos0 + r;
-      const int lo = chunk > 0 ? (qp / chunk) * chunk : 0;
+      const int lo = first_key(qp, chunk, window);
       float mt = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -342,7 +354,8 @@ __global__ void __launch_bounds__(32 * kAW)
 sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                       const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
                       const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
-                      int Hq, int G, int d, int dv, float scale, int chunk, const int* __restrict__ atoms) {
+                      int Hq, int G, int d, int dv, float scale, int chunk, int window, int kpitch, int vpitch,
+                      const int* __restrict__ atoms) {
   // q [REP][d8] | partial values [kAW][REP][dv] | partial max [kAW][REP] | partial sum [kAW][REP] | key staging
   extern __shared__ __align__(16) float qs[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -368,8 +381,8 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
   __syncthreads();
   const int g = h0 / (Hq / G);
   const int* tab = tables + (long long)seq * max_blocks;
-  const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
-  const bool kvec = d % 8 == 0, vvec = dv % 4 == 0;
+  const int lo = first_key(pos, chunk, window);
+  const bool kvec = d % 8 == 0 && kpitch % 8 == 0, vvec = dv % 4 == 0 && vpitch % 4 == 0;
   float m[REP], l[REP], acc[REP][VPL];
 #pragma unroll
   for (int hh = 0; hh < REP; ++hh) {
@@ -399,7 +412,7 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
             const int i = lane + 32 * (i0 + x), r = i / per, cc = (i % per) * E;
             const long long slot = __shfl_sync(0xffffffffu, myslot, r);
             u[x] = make_uint4(0u, 0u, 0u, 0u);
-            if (slot >= 0) u[x] = *reinterpret_cast<const uint4*>(kcache + (slot * G + g) * d + c0 + cc);
+            if (slot >= 0) u[x] = *reinterpret_cast<const uint4*>(kcache + slot * kpitch + g * d + c0 + cc);
           }
 #pragma unroll
           for (int x = 0; x < kKeyLoads; ++x) {
@@ -421,7 +434,7 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
       }
     } else if (j <= pos) {
 #pragma unroll
-      for (int hh = 0; hh < REP; ++hh) sc[hh] = dot_row<T>(qs + hh * d8, kcache + (myslot * G + g) * d, d, false);
+      for (int hh = 0; hh < REP; ++hh) sc[hh] = dot_row<T>(qs + hh * d8, kcache + myslot * kpitch + g * d, d, false);
     }
     float p[REP];
 #pragma unroll
@@ -441,7 +454,7 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
 #pragma unroll
         for (int u = 0; u < kValLoads; ++u) {
           const long long slot = __shfl_sync(0xffffffffu, myslot, min(jj + u, n - 1));
-          const T* vr = vcache + (slot * G + g) * dv;
+          const T* vr = vcache + slot * vpitch + g * dv;
 #pragma unroll
           for (int i = 0; i < VPL / 4; ++i) {
             const int c = 128 * i + 4 * lane;
@@ -463,7 +476,7 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
     } else {                                         // lane holds channels lane + 32 i
       for (int jj = 0; jj < n; ++jj) {
         const long long slot = __shfl_sync(0xffffffffu, myslot, jj);
-        const T* vr = vcache + (slot * G + g) * dv;
+        const T* vr = vcache + slot * vpitch + g * dv;
 #pragma unroll
         for (int hh = 0; hh < REP; ++hh) {
           const float pj = __shfl_sync(0xffffffffu, p[hh], jj);
@@ -506,7 +519,7 @@ template <typename T, int REP, int VPL>
 static int launch_attention_rows_v(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
                                    void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                                    int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale,
-                                   int chunk, const int* atoms, cudaStream_t s) {
+                                   int chunk, int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
   const size_t smem = (size_t)(REP * ((d + 7) & ~7) + kAW * REP * dv + 2 * kAW * REP + kAW * 32 * 68) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sink_attention_kernel<T, REP, VPL>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -514,7 +527,8 @@ static int launch_attention_rows_v(dim3 grid, const void* q, const void* kcache,
   grid.y = Hq / REP;
   sink_attention_kernel<T, REP, VPL><<<grid, 32 * kAW, smem, s>>>(
       (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)tok_seq,
-      (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, atoms);
+      (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, kpitch,
+      vpitch, atoms);
   return SXB_OK;
 }
 
@@ -522,25 +536,27 @@ template <typename T, int REP>
 static int launch_attention_rows(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
                                  void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                                  int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
-                                 const int* atoms, cudaStream_t s) {
+                                 int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
   if (dv <= 128)
     return launch_attention_rows_v<T, REP, 4>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos, tables, max_blocks,
-                                              block_size, Hq, G, d, dv, scale, chunk, atoms, s);
+                                              block_size, Hq, G, d, dv, scale, chunk, window, kpitch, vpitch, atoms,
+                                              s);
   return launch_attention_rows_v<T, REP, kMaxVPerLane>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos, tables,
-                                                       max_blocks, block_size, Hq, G, d, dv, scale, chunk, atoms, s);
+                                                       max_blocks, block_size, Hq, G, d, dv, scale, chunk, window,
+                                                       kpitch, vpitch, atoms, s);
 }
 
 // Query heads per key/value head that one CTA takes together: the largest of 8, 4, 2, 1 that divides the group.
 static int attention_rows(int dtype, dim3 grid, const void* q, const void* kcache, const void* vcache,
                           const void* sink, void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                           int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
-                          const int* atoms, cudaStream_t s) {
+                          int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
   const int group = Hq / G;
   int rc = SXB_OK;
 #define ROWS(REP)                                                                                                      \
   SEQMIX_DISPATCH(dtype, (rc = launch_attention_rows<T, REP>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos,      \
                                                               tables, max_blocks, block_size, Hq, G, d, dv, scale,      \
-                                                              chunk, atoms, s)))
+                                                              chunk, window, kpitch, vpitch, atoms, s)))
   if (group % 8 == 0) ROWS(8);
   else if (group % 4 == 0) ROWS(4);
   else if (group % 2 == 0) ROWS(2);
@@ -940,14 +956,292 @@ gated_act_rows_kernel(const T* __restrict__ in, T* __restrict__ out, long long t
   out[i] = from_f32<T>(a * up);
 }
 
+
+// ------------------------------------------------------------------------------------------------ post-norm layers
+// Layers of the form  x <- x + scale (.) (sublayer(x + conv(x)) / rms * gain):  the sublayer reads the fp32 stream
+// through a short causal filter with a skip path, its output is normalised with ONE gain for all channels and scaled
+// per channel before it joins the stream; the stream a layer hands on may be a learned mixture of the embedding and
+// all layers' results so far.
+
+// out[t, c] = x[t, c] + sum_j w[c, taps-1-j] x[t-j, c]; x fp32, rows before this batch from the slot's carried inputs
+// (state fp32 [slots, taps-1, C], last row = most recent), rows before the sequence's start are zero.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_residual_kernel(const float* __restrict__ x, const T* __restrict__ w, const float* __restrict__ state,
+                     const int* __restrict__ seq_info, const int* __restrict__ tok_seq, T* __restrict__ out, int C,
+                     int taps) {
+  const int t = blockIdx.x;
+  const int* si = seq_info + 4 * tok_seq[t];
+  const int local = t - si[0], seen = si[2];
+  const float* st = state + (long long)si[3] * (taps - 1) * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    const T* wc = w + (long long)c * taps;
+    const float cur = x[(long long)t * C + c];
+    float acc = 0.f;
+    for (int j = taps - 1; j >= 1; --j) {            // oldest input first
+      const int src = local - j;
+      float v = 0.f;
+      if (src >= 0) v = x[(long long)(t - j) * C + c];
+      else if (seen + src >= 0) v = st[(long long)(taps - 1 + src) * C + c];
+      acc += to_f32<T>(wc[taps - 1 - j]) * v;
+    }
+    acc += to_f32<T>(wc[taps - 1]) * cur;
+    out[(long long)t * C + c] = from_f32<T>(cur + acc);
+  }
+}
+
+// One CTA per row: v = x_in + ls (.) (y / rms(y) * gain) -> x_out (may be x_in); with mix_out:
+// mix_out = sum_{j < n_prev} mixw[j] stack[j] + mixw[n_prev] v  (stack[j] = fp32 rows at stack + j * stack_stride).
+template <typename T>
+__global__ void __launch_bounds__(256)
+post_norm_mix_kernel(const float* __restrict__ x_in, const T* __restrict__ y, const float* __restrict__ gain,
+                     const float* __restrict__ ls, float* __restrict__ x_out, const float* __restrict__ stack,
+                     long long stack_stride, int n_prev, const float* __restrict__ mixw, float* __restrict__ mix_out,
+                     int width, float eps) {
+  __shared__ float red[32];
+  const long long base = (long long)blockIdx.x * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_f32<T>(y[base + c]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)width + eps);
+  const float g = gain[0];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = x_in[base + c] + to_f32<T>(y[base + c]) * inv * g * ls[c];
+    x_out[base + c] = v;
+    if (mix_out != nullptr) {
+      float m = 0.f;
+      for (int j = 0; j < n_prev; ++j) m += mixw[j] * stack[j * stack_stride + base + c];
+      mix_out[base + c] = m + mixw[n_prev] * v;
+    }
+  }
+}
+
+// out[i] = x[rows[i]] / rms * gain (one gain for all channels); rows null: every row in order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_scale_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gain,
+                      T* __restrict__ out, int width, float eps) {
+  __shared__ float red[32];
+  const float* r = x + (long long)(rows ? rows[blockIdx.x] : blockIdx.x) * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) ss += r[c] * r[c];
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)width + eps);
+  const float g = gain[0];
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(long long)blockIdx.x * width + c] = from_f32<T>(r[c] * inv * g);
+}
+
+// out [rows, n] = x[:, :n] / rms * w for rows of pitch ld.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rms_norm_slice_kernel(const T* __restrict__ x, long long ld, const T* __restrict__ w, T* __restrict__ out, int n,
+                      float eps) {
+  __shared__ float red[32];
+  const T* r = x + (long long)blockIdx.x * ld;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = to_f32<T>(r[c]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x)
+    out[(long long)blockIdx.x * n + c] = from_f32<T>(to_f32<T>(r[c]) * inv * to_f32<T>(w[c]));
+}
+
+// out = act(in + bias) for rows of any width; act as in gated_act_rows plus 4 = relu(z)^2.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_act_rows_kernel(const T* __restrict__ in, const T* __restrict__ bias, T* __restrict__ out, long long total, int F,
+                     int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float z = to_f32<T>(in[i]) + (bias ? to_f32<T>(bias[i % F]) : 0.f);
+  float a;
+  if (act == 4) {
+    const float r = fmaxf(z, 0.f);
+    a = r * r;
+  } else if (act == 2) {
+    a = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  } else if (act == 3) {
+    a = silu_f(z);
+  } else if (act == 1) {
+    a = fmaxf(z, 0.f);
+  } else {
+    a = z;
+  }
+  out[i] = from_f32<T>(a);
+}
+
+// ------------------------------------------------------------------------------------------------ latent attention
+// Keys and values are up-projections of one latent vector per token, so the cache holds the normalised latent (r
+// channels) followed by one rotated key part (rot channels) that all heads share; a query head meets them as
+// [q_abs | q_rot], q_abs its unrotated part carried through the key up-projection.  One CTA per token:
+//   cache[slot] = [ latent / rms * w_norm | rope(k_rot) ],  q_out[t, h] = [ q_abs[t, h] | rope(q[t, h, dim:]) ]  (fp32)
+// rope turns the pairs (2i, 2i+1), i < rot_dims / 2, by pos * inv_freq[i]; channels from rot_dims on pass unchanged.
+template <typename T>
+__device__ __forceinline__ void rope_pairs(const T* __restrict__ src, int rot, int rot_dims, float pos,
+                                           const float* __restrict__ inv_freq, int lane, int stride, float* dst32,
+                                           T* dstT) {
+  for (int i = lane; i < rot; i += stride) {
+    float v = to_f32<T>(src[i]);
+    if (i < rot_dims) {
+      float sn, cs;
+      sincosf(pos * inv_freq[i >> 1], &sn, &cs);
+      const float other = to_f32<T>(src[i ^ 1]);
+      v = (i & 1) ? v * cs + other * sn : v * cs - other * sn;
+    }
+    if (dst32) dst32[i] = v;
+    else dstT[i] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_qk_prepare_kernel(const T* __restrict__ qfull, long long ldq, const T* __restrict__ qabs, long long qa_tok,
+                         long long qa_head, const T* __restrict__ kv, long long ldkv, const T* __restrict__ w_norm,
+                         const float* __restrict__ inv_freq, float* __restrict__ q_out, T* __restrict__ cache,
+                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                         const int* __restrict__ tables, int max_blocks, int block_size, int H, int dim, int rot, int r,
+                         int rot_dims, float eps) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int p = tok_pos[t];
+  const float pos = (float)p;
+  const long long page = tables[(long long)tok_seq[t] * max_blocks + p / block_size];
+  T* crow = cache + (page * block_size + p % block_size) * (long long)(r + rot);
+  const T* kr = kv + (long long)t * ldkv;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < r; c += blockDim.x) {
+    const float v = to_f32<T>(kr[c]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)r + eps);
+  for (int c = threadIdx.x; c < r; c += blockDim.x)
+    crow[c] = from_f32<T>(to_f32<T>(kr[c]) * inv * to_f32<T>(w_norm[c]));
+  rope_pairs<T>(kr + r, rot, rot_dims, pos, inv_freq, threadIdx.x, blockDim.x, nullptr, crow + r);
+  const int d = r + rot;
+  for (int h = warp; h < H; h += nw) {
+    float* qo = q_out + ((long long)t * H + h) * d;
+    const T* qa = qabs + (long long)t * qa_tok + (long long)h * qa_head;
+    for (int c = lane; c < r; c += 32) qo[c] = to_f32<T>(qa[c]);
+    rope_pairs<T>(qfull + (long long)t * ldq + (long long)h * (dim + rot) + dim, rot, rot_dims, pos, inv_freq, lane, 32,
+                  qo + r, nullptr);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ matrix-memory LSTM
+// Per head, with log gates i, f and a running maximum m (0 for a new sequence):
+//   m_t = max(f_t + m_(t-1), i_t);  S_t = exp(f_t + m_(t-1) - m_t) S_(t-1) + exp(i_t - m_t) k_t v_t^T;  n_t likewise with k_t;
+//   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
+// The normaliser n rides along as one more value channel that is always 1, so the recurrence itself is
+// linear_recurrence with decay = exp(f + m_prev - m), write strength = exp(i - m) and dv + 1 channels.
+
+// buf fp32 [rows, 2 H n + H (dv + 1)] = [ q * qscale | k | per head (v, 1) ] from projection rows [q | k | v | ...].
+template <typename T>
+__global__ void __launch_bounds__(256)
+mlstm_prepare_kernel(const T* __restrict__ proj, long long ld, float* __restrict__ buf, int H, int n, int dv,
+                     float qscale) {
+  const int t = blockIdx.x;
+  const T* row = proj + (long long)t * ld;
+  const int nq = H * n, wide = 2 * nq + H * (dv + 1);
+  float* o = buf + (long long)t * wide;
+  for (int c = threadIdx.x; c < wide; c += blockDim.x) {
+    float v;
+    if (c < nq) v = to_f32<T>(row[c]) * qscale;
+    else if (c < 2 * nq) v = to_f32<T>(row[c]);
+    else {
+      const int h = (c - 2 * nq) / (dv + 1), e = (c - 2 * nq) % (dv + 1);
+      v = e == dv ? 1.f : to_f32<T>(row[2 * nq + h * dv + e]);
+    }
+    o[c] = v;
+  }
+}
+
+// One warp per (sequence, head): gates of 32 tokens at a time, the running maximum through a warp scan of the maps
+// m -> max(m + f, i).  i = cap tanh((raw_i + b_i) / cap), f = logsigmoid(cap tanh((raw_f + b_f) / cap)).
+template <typename T>
+__global__ void __launch_bounds__(32)
+mlstm_gate_scan_kernel(const T* __restrict__ raw_i, const T* __restrict__ raw_f, long long ld,
+                       const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
+                       float* __restrict__ mstate, float* __restrict__ decay, float* __restrict__ beta,
+                       float* __restrict__ mt, const int* __restrict__ seq_info, int H) {
+  const int* si = seq_info + 4 * blockIdx.x;
+  const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
+  const int h = blockIdx.y, lane = threadIdx.x;
+  float m = seen > 0 ? mstate[(long long)slot * H + h] : 0.f;
+  const float bi = bias_i[h], bf = bias_f[h];
+  for (int t0 = 0; t0 < rows; t0 += 32) {
+    const int t = t0 + lane;
+    const bool valid = t < rows;
+    float ig = -INFINITY, fg = 0.f;
+    if (valid) {
+      const long long o = (long long)(first + t) * ld + h;
+      ig = cap * tanhf((to_f32<T>(raw_i[o]) + bi) / cap);
+      const float fr = cap * tanhf((to_f32<T>(raw_f[o]) + bf) / cap);
+      fg = fminf(fr, 0.f) - log1pf(expf(-fabsf(fr)));
+    }
+    float a = fg, b = ig;                           // the map m -> max(m + a, b) of tokens t0 .. t
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float ap = __shfl_up_sync(0xffffffffu, a, off), bp = __shfl_up_sync(0xffffffffu, b, off);
+      if (lane >= off) {
+        b = fmaxf(bp + a, b);
+        a = ap + a;
+      }
+    }
+    const float mcur = fmaxf(m + a, b);
+    float mprev = __shfl_up_sync(0xffffffffu, mcur, 1);
+    if (lane == 0) mprev = m;
+    if (valid) {
+      const long long o = (long long)(first + t) * H + h;
+      decay[o] = expf(fg + mprev - mcur);
+      beta[o] = expf(ig - mcur);
+      mt[o] = mcur;
+    }
+    m = __shfl_sync(0xffffffffu, mcur, 31);         // lanes past the end hold the identity map: m of the last token
+  }
+  if (lane == 0) mstate[(long long)slot * H + h] = m;
+}
+
+// One warp per (token, head): o fp32 [rows, H (dv + 1)] -> out = unit_rms(o[:dv] / (max(|o[dv]|, exp(-m)) + 1e-6)) * w *
+// sigmoid(gate).
+template <typename T>
+__global__ void __launch_bounds__(128)
+mlstm_output_kernel(const float* __restrict__ o, const float* __restrict__ mt, const T* __restrict__ gate,
+                    long long ldg, const T* __restrict__ w, T* __restrict__ out, int n_tokens, int H, int dv,
+                    float eps) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= n_tokens * H) return;
+  const int t = idx / H, h = idx % H;
+  const float* r = o + ((long long)t * H + h) * (dv + 1);
+  const float den = fmaxf(fabsf(r[dv]), expf(-mt[idx])) + 1e-6f;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) {
+    const float v = r[c] / den;
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int c = lane; c < dv; c += 32) {
+    const float g = sigmoid_f(to_f32<T>(gate[(long long)t * ldg + h * dv + c]));
+    out[(long long)t * H * dv + h * dv + c] = from_f32<T>(r[c] / den * inv * to_f32<T>(w[h * dv + c]) * g);
+  }
+}
+
 }  // namespace seqmix
 }  // namespace sxb
 
 using namespace sxb;
 using namespace sxb::seqmix;
 
-/* out fp32 [n_tokens, width] = table[ids[t]] * scale + p, p[2i] = sin(pos * base^(-2i/width)), p[2i+1] = cos(same).
- * table: `dtype` [vocab, width]. */
+/* out fp32 [n_tokens, width] = table[ids[t]] * scale + p, p[2i] = sin(pos * base^(-2i/width)), p[2i+1] = cos(same);
+ * base <= 0: p = 0.  table: `dtype` [vocab, width]. */
 SXB_API int sxb_embed_sinusoid(const void* ids, const void* pos, const void* table, void* out, int n_tokens, int width,
                                float scale, float base, int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
@@ -987,17 +1281,23 @@ SXB_API int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, 
   return SXB_OK;
 }
 
-/* Attention of every token over the cached keys lo..pos of its sequence (lo = start of its chunk of `chunk` positions,
- * or 0 when chunk == 0), scores and weights in fp32; sink (fp32 [Hq] or null) adds exp(sink[h]) to the denominator.
- * out `dtype` [n_tokens, Hq * dv] (the caches have the same type).  One CTA per (token, head). */
+/* Attention of every token over the cached keys lo..pos of its sequence, scores and weights in fp32.  lo = start of the
+ * token's chunk of `chunk` positions (chunk > 0), else pos - window + 1 clamped at 0 (window > 0), else 0.  sink (fp32
+ * [Hq] or null) adds exp(sink[h]) to the denominator.  Key rows sit at kcache + slot * k_pitch + g * d and value rows at
+ * vcache + slot * v_pitch + g * dv (pitches in elements; 0 = packed [pages, block_size, G, d|dv]), so values may be a
+ * column range of the key rows.  out `dtype` [n_tokens, Hq * dv] (the caches have the same type).  One CTA per
+ * (token, head group). */
 SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
                                int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
-                               int dtype, void* stream) {
+                               int window, int k_pitch, int v_pitch, int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
   if (dv > 32 * kMaxVPerLane || Hq % G) return SXB_ERR_UNSUPPORTED;
+  if (k_pitch <= 0) k_pitch = G * d;
+  if (v_pitch <= 0) v_pitch = G * dv;
   const int rc = attention_rows(dtype, dim3(n_tokens, 1), q, kcache, vcache, sink, out, tok_seq, tok_pos, tables,
-                                max_blocks, block_size, Hq, G, d, dv, scale, chunk, nullptr, (cudaStream_t)stream);
+                                max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, k_pitch, v_pitch, nullptr,
+                                (cudaStream_t)stream);
   if (rc != SXB_OK) return rc;
   SXB_CHECK_LAUNCH();
   return SXB_OK;
@@ -1006,33 +1306,38 @@ SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vc
 template <typename T, int NV>
 static int launch_attention_tiles(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                   const void* atoms, int n_long, const void* tables, int max_blocks, int block_size,
-                                  int Hq, int G, int d, int dv, float scale, int chunk, cudaStream_t s) {
+                                  int Hq, int G, int d, int dv, float scale, int chunk, int window, int kpitch,
+                                  int vpitch, cudaStream_t s) {
   const size_t smem = (size_t)(kBQ * (d + 4) + std::max(kBK * (d + 4), kBQ * (kBK + 4)) + kBK * NV * 64) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sink_attention_tile_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
   sink_attention_tile_kernel<T, NV><<<dim3(2 * n_long, Hq), 256, smem, s>>>(
       (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)atoms,
-      (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk);
+      (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, kpitch, vpitch);
   return SXB_OK;
 }
 
 /* The same attention scheduled by attention atoms int32 [n_atoms, 6] = (sequence, first row, queries, first position,
  * -, -), longest first: the first n_long atoms (more than 16 queries, at most 128) run the tiled kernel, 64 queries per
- * CTA; the others one warp per (query, head).  Needs d and dv multiples of 4 and at most 256. */
+ * CTA; the others one warp per (query, head).  Needs d, dv and both pitches multiples of 4, d and dv at most 256. */
 SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                      const void* atoms, int n_atoms, int n_long, const void* tables, int max_blocks,
-                                     int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int dtype,
-                                     void* stream) {
+                                     int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int window,
+                                     int k_pitch, int v_pitch, int dtype, void* stream) {
   if (n_atoms <= 0) return SXB_OK;
-  if (d % 4 || dv % 4 || d > 256 || dv > 256 || Hq % G || n_long < 0 || n_long > n_atoms) return SXB_ERR_UNSUPPORTED;
+  if (k_pitch <= 0) k_pitch = G * d;
+  if (v_pitch <= 0) v_pitch = G * dv;
+  if (d % 4 || dv % 4 || k_pitch % 4 || v_pitch % 4 || d > 256 || dv > 256 || Hq % G || n_long < 0 || n_long > n_atoms)
+    return SXB_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   if (n_long > 0) {
     const int nv = (dv + 63) / 64;
     int rc = SXB_OK;
 #define TILES(NV)                                                                                                     \
   SEQMIX_DISPATCH(dtype, (rc = launch_attention_tiles<T, NV>(q, kcache, vcache, sink, out, atoms, n_long, tables,      \
-                                                              max_blocks, block_size, Hq, G, d, dv, scale, chunk, s)))
+                                                              max_blocks, block_size, Hq, G, d, dv, scale, chunk,      \
+                                                              window, k_pitch, v_pitch, s)))
     if (nv == 1) TILES(1);
     else if (nv == 2) TILES(2);
     else if (nv == 3) TILES(3);
@@ -1043,8 +1348,8 @@ SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const vo
   }
   if (n_atoms > n_long) {
     const int rc = attention_rows(dtype, dim3((n_atoms - n_long) * kShortAtom, 1), q, kcache, vcache, sink, out, nullptr,
-                                  nullptr, tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk,
-                                  (const int*)atoms + 6 * n_long, s);
+                                  nullptr, tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, k_pitch,
+                                  v_pitch, (const int*)atoms + 6 * n_long, s);
     if (rc != SXB_OK) return rc;
     SXB_CHECK_LAUNCH();
   }
@@ -1171,6 +1476,126 @@ SXB_API int sxb_gated_act_rows(const void* in, void* out, long long rows, int F,
   if (total <= 0) return SXB_OK;
   SEQMIX_DISPATCH(dtype, (gated_act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                              (const T*)in, (T*)out, total, F, act)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out `dtype` [n_tokens, C] = x + causal filter of x over time per channel: x fp32 [n_tokens, C], w `dtype` [C, taps]
+ * (last tap = current token), carried inputs state fp32 [slots, taps-1, C] (update them with sxb_conv_state_update,
+ * dtype fp32, afterwards). */
+SXB_API int sxb_conv_residual(const void* x, const void* w, const void* state, const void* seq_info,
+                              const void* tok_seq, void* out, int n_tokens, int C, int taps, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (taps < 1) return SXB_ERR_BAD_ARG;
+  dim3 grid(n_tokens, (C + 1023) / 1024);
+  SEQMIX_DISPATCH(dtype, (conv_residual_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+                             (const float*)x, (const T*)w, (const float*)state, (const int*)seq_info,
+                             (const int*)tok_seq, (T*)out, C, taps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Per row: v = x_in + ls (.) (y / rms(y) * gain[0]) -> x_out (fp32, may alias x_in); y `dtype`, gain / ls fp32.  With
+ * mix_out (fp32): mix_out = sum_{j < n_prev} mixw[j] * (stack + j * stack_stride)[row] + mixw[n_prev] * v. */
+SXB_API int sxb_post_norm_mix(const void* x_in, const void* y, const void* gain, const void* ls, void* x_out,
+                              const void* stack, long long stack_stride, int n_prev, const void* mixw, void* mix_out,
+                              long long rows, int width, float eps, int dtype, void* stream) {
+  if (rows <= 0) return SXB_OK;
+  if (mix_out != nullptr && (mixw == nullptr || (n_prev > 0 && stack == nullptr))) return SXB_ERR_BAD_ARG;
+  SEQMIX_DISPATCH(dtype, (post_norm_mix_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+                             (const float*)x_in, (const T*)y, (const float*)gain, (const float*)ls, (float*)x_out,
+                             (const float*)stack, stack_stride, n_prev, (const float*)mixw, (float*)mix_out, width,
+                             eps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out `dtype` [n_rows, width] = x[rows[i]] / rms * gain[0]; x fp32, rows int32 or null (all rows in order). */
+SXB_API int sxb_rms_scale_rows(const void* x, const void* rows, const void* gain, void* out, int n_rows, int width,
+                               float eps, int dtype, void* stream) {
+  if (n_rows <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (rms_scale_rows_kernel<T><<<n_rows, 256, 0, (cudaStream_t)stream>>>(
+                             (const float*)x, (const int*)rows, (const float*)gain, (T*)out, width, eps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out `dtype` [n_tokens, n] = x[:, :n] / rms * w; x rows of pitch ld. */
+SXB_API int sxb_rms_norm_slice(const void* x, long long ld, const void* w, void* out, int n_tokens, int n, float eps,
+                               int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (rms_norm_slice_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
+                             (const T*)x, ld, (const T*)w, (T*)out, n, eps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out = act(in + bias) over rows of F channels; act: 0 identity, 1 relu, 2 gelu (tanh form), 3 silu, 4 relu squared. */
+SXB_API int sxb_bias_act_rows(const void* in, const void* bias, void* out, long long rows, int F, int act, int dtype,
+                              void* stream) {
+  const long long total = rows * F;
+  if (total <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (bias_act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)in, (const T*)bias, (T*)out, total, F, act)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Latent attention, per token: cache[page, offset] = [kv[:r] / rms * w_norm | rope(kv[r : r+rot])] (`dtype`
+ * [pages, block_size, r + rot]); q_out fp32 [n_tokens, H, r + rot] = [qabs[t, h] | rope(qfull[t, h, dim : dim+rot])].
+ * qfull rows of pitch ldq hold H heads of dim + rot; qabs element (t, h, c) at t * qa_tok + h * qa_head + c; kv rows of
+ * pitch ldkv; inv_freq fp32 [rot_dims / 2]. */
+SXB_API int sxb_latent_qk_prepare(const void* qfull, long long ldq, const void* qabs, long long qa_tok,
+                                  long long qa_head, const void* kv, long long ldkv, const void* w_norm,
+                                  const void* inv_freq, void* q_out, void* cache, const void* tok_seq,
+                                  const void* tok_pos, const void* tables, int n_tokens, int max_blocks, int block_size,
+                                  int H, int dim, int rot, int r, int rot_dims, float eps, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (rot_dims > rot || (rot_dims & 1)) return SXB_ERR_BAD_ARG;
+  SEQMIX_DISPATCH(dtype, (latent_qk_prepare_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
+                             (const T*)qfull, ldq, (const T*)qabs, qa_tok, qa_head, (const T*)kv, ldkv,
+                             (const T*)w_norm, (const float*)inv_freq, (float*)q_out, (T*)cache, (const int*)tok_seq,
+                             (const int*)tok_pos, (const int*)tables, max_blocks, block_size, H, dim, rot, r, rot_dims,
+                             eps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* buf fp32 [n_tokens, 2 H n + H (dv + 1)] = [q * qscale | k | per head (v, 1)] from projection rows (pitch ld) that
+ * start with q (H n) | k (H n) | v (H dv). */
+SXB_API int sxb_mlstm_prepare(const void* proj, long long ld, void* buf, int n_tokens, int H, int n, int dv,
+                              float qscale, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (mlstm_prepare_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)proj, ld, (float*)buf, H, n, dv, qscale)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Gates of the matrix-memory LSTM: raw_i / raw_f (`dtype`, pitch ld, H channels), biases fp32 [H]; i = cap tanh((raw_i +
+ * b_i) / cap), f = logsigmoid(cap tanh((raw_f + b_f) / cap)); m_t = max(f_t + m_(t-1), i_t) from mstate fp32 [slots, H]
+ * (0 for a sequence that has seen no token; written back).  decay = exp(f + m_(t-1) - m_t), beta = exp(i - m_t), mt = m_t,
+ * all fp32 [rows, H]. */
+SXB_API int sxb_mlstm_gate_scan(const void* raw_i, const void* raw_f, long long ld, const void* bias_i,
+                                const void* bias_f, float cap, void* mstate, void* decay, void* beta, void* mt,
+                                const void* seq_info, int n_seqs, int H, int dtype, void* stream) {
+  if (n_seqs <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (mlstm_gate_scan_kernel<T><<<dim3(n_seqs, H), 32, 0, (cudaStream_t)stream>>>(
+                             (const T*)raw_i, (const T*)raw_f, ld, (const float*)bias_i, (const float*)bias_f, cap,
+                             (float*)mstate, (float*)decay, (float*)beta, (float*)mt, (const int*)seq_info, H)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out `dtype` [n_tokens, H dv]: per head unit_rms(o[:dv] / (max(|o[dv]|, exp(-mt)) + 1e-6)) * w * sigmoid(gate); o fp32
+ * [n_tokens, H (dv + 1)], gate `dtype` rows of pitch ldg, w `dtype` [H dv]. */
+SXB_API int sxb_mlstm_output(const void* o, const void* mt, const void* gate, long long ldg, const void* w, void* out,
+                             int n_tokens, int H, int dv, float eps, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  const int total = n_tokens * H;
+  SEQMIX_DISPATCH(dtype, (mlstm_output_kernel<T><<<(total + 3) / 4, 128, 0, (cudaStream_t)stream>>>(
+                             (const float*)o, (const float*)mt, (const T*)gate, ldg, (const T*)w, (T*)out, n_tokens, H,
+                             dv, eps)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

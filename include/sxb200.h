@@ -457,8 +457,8 @@ int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, void* q_
                        void* stream);
 int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                        const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens, int max_blocks,
-                       int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int dtype,
-                       void* stream);
+                       int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int window,
+                       int k_pitch, int v_pitch, int dtype, void* stream);
 int sxb_conv_silu(const void* x, long long ld, const void* w, const void* bias, const void* state,
                   const void* seq_info, const void* tok_seq, void* out, int n_tokens, int C, int taps, int dtype,
                   void* stream);
@@ -479,8 +479,40 @@ int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act
 /* ---- csrc/seq_mixers.cu */
 int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                              const void* atoms, int n_atoms, int n_long, const void* tables, int max_blocks,
-                             int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int dtype,
-                             void* stream);
+                             int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int window,
+                             int k_pitch, int v_pitch, int dtype, void* stream);
+
+/* ---- csrc/moe_ragged.cu */
+/* As sxb_moe_scatter with every copied row multiplied by its routing weight: moe_input[slot(t, k)] = x[t] * scores[t, k].
+ * x / moe_input `dtype` (bf16 or fp32) of any width, scores fp32 [T, K]. */
+int sxb_moe_scatter_scaled(const void* x, const void* scores, void* moe_input, const void* assignments,
+                           const void* offsets, const void* expert_counts, void* expert_cumsum, void* mapped_slots,
+                           int n_tokens, int n_experts, int top_k, int hidden, int dtype, void* stream);
+
+/* ---- csrc/seq_mixers.cu */
+int sxb_conv_residual(const void* x, const void* w, const void* state, const void* seq_info, const void* tok_seq,
+                      void* out, int n_tokens, int C, int taps, int dtype, void* stream);
+int sxb_post_norm_mix(const void* x_in, const void* y, const void* gain, const void* ls, void* x_out,
+                      const void* stack, long long stack_stride, int n_prev, const void* mixw, void* mix_out,
+                      long long rows, int width, float eps, int dtype, void* stream);
+int sxb_rms_scale_rows(const void* x, const void* rows, const void* gain, void* out, int n_rows, int width,
+                       float eps, int dtype, void* stream);
+int sxb_rms_norm_slice(const void* x, long long ld, const void* w, void* out, int n_tokens, int n, float eps,
+                       int dtype, void* stream);
+int sxb_bias_act_rows(const void* in, const void* bias, void* out, long long rows, int F, int act, int dtype,
+                      void* stream);
+int sxb_latent_qk_prepare(const void* qfull, long long ldq, const void* qabs, long long qa_tok, long long qa_head,
+                          const void* kv, long long ldkv, const void* w_norm, const void* inv_freq, void* q_out,
+                          void* cache, const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
+                          int max_blocks, int block_size, int H, int dim, int rot, int r, int rot_dims, float eps,
+                          int dtype, void* stream);
+int sxb_mlstm_prepare(const void* proj, long long ld, void* buf, int n_tokens, int H, int n, int dv, float qscale,
+                      int dtype, void* stream);
+int sxb_mlstm_gate_scan(const void* raw_i, const void* raw_f, long long ld, const void* bias_i, const void* bias_f,
+                        float cap, void* mstate, void* decay, void* beta, void* mt, const void* seq_info,
+                        int n_seqs, int H, int dtype, void* stream);
+int sxb_mlstm_output(const void* o, const void* mt, const void* gate, long long ldg, const void* w, void* out,
+                     int n_tokens, int H, int dv, float eps, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

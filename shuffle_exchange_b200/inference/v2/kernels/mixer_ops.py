@@ -20,8 +20,8 @@ _lib.register({
     "sxb_embed_sinusoid": "pppp" "ii" "ff" "i" "p",
     "sxb_resid_norm_step": "pppppp" "l" "i" "f" "i" "p",
     "sxb_qk_norm_append": "p" "l" "ppppppp" "iiiiiii" "f" "ii" "p",
-    "sxb_sink_attention": "pppppppp" "iiiiiii" "f" "ii" "p",
-    "sxb_sink_attention_atoms": "pppppp" "ii" "p" "iiiiii" "f" "ii" "p",
+    "sxb_sink_attention": "pppppppp" "iiiiiii" "f" "iiiii" "p",
+    "sxb_sink_attention_atoms": "pppppp" "ii" "p" "iiiiii" "f" "iiiii" "p",
     "sxb_conv_silu": "p" "l" "pppppp" "iii" "i" "p",
     "sxb_conv_state_update": "p" "l" "pp" "iii" "i" "p",
     "sxb_unit_norm_heads": "p" "l" "iii" "ff" "i" "p",
@@ -29,9 +29,18 @@ _lib.register({
     "sxb_linear_recurrence": "pp" "l" "p" "l" "pppppp" "iiiiii" "p",
     "sxb_group_norm_gate": "pp" "l" "p" "i" "p" "iii" "f" "i" "i" "p",
     "sxb_gated_act_rows": "pp" "l" "ii" "i" "p",
+    "sxb_conv_residual": "pppppp" "iii" "i" "p",
+    "sxb_post_norm_mix": "pppppp" "l" "i" "pp" "l" "i" "f" "i" "p",
+    "sxb_rms_scale_rows": "pppp" "ii" "f" "i" "p",
+    "sxb_rms_norm_slice": "p" "l" "pp" "ii" "f" "i" "p",
+    "sxb_bias_act_rows": "ppp" "l" "ii" "i" "p",
+    "sxb_latent_qk_prepare": "p" "l" "p" "ll" "p" "l" "ppppppp" "iii" "iiiii" "f" "i" "p",
+    "sxb_mlstm_prepare": "p" "l" "p" "iiii" "f" "i" "p",
+    "sxb_mlstm_gate_scan": "pp" "l" "pp" "f" "ppppp" "ii" "i" "p",
+    "sxb_mlstm_output": "ppp" "l" "pp" "iii" "f" "i" "p",
 })
 
-_ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3}
+_ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3, "relu_sq": 4}
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -47,14 +56,17 @@ def _rows(t: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------------ embedding
 def embed_sinusoid(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, scale: float,
-                   base: float = 10000.0) -> torch.Tensor:
-    """fp32 ``[T, width]``: ``table[ids] * scale + p`` with ``p[2i] = sin(pos * base^(-2i/width))``, ``p[2i+1] = cos``."""
+                   base: Optional[float] = 10000.0) -> torch.Tensor:
+    """fp32 ``[T, width]``: ``table[ids] * scale + p`` with ``p[2i] = sin(pos * base^(-2i/width))``, ``p[2i+1] = cos``;
+    ``base`` None: no position vector."""
     T, W = ids.numel(), table.shape[1]
     if table.is_cuda:
         out = torch.empty(T, W, dtype=torch.float32, device=table.device)
         _lib.call("sxb_embed_sinusoid", ids.data_ptr(), positions.data_ptr(), table.data_ptr(), out.data_ptr(), T, W,
-                  float(scale), float(base), _dt(table), _lib.stream_ptr())
+                  float(scale), 0.0 if base is None else float(base), _dt(table), _lib.stream_ptr())
         return out
+    if base is None:
+        return table[ids.long()].float() * scale
     i = torch.arange(W, device=table.device) // 2
     freq = torch.exp2(-(2.0 * i.float() / W) * math.log2(base))
     ang = positions.float()[:, None] * freq[None, :]
@@ -125,38 +137,58 @@ def tiles_supported(d: int, dv: int) -> bool:
 
 def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, sink: Optional[torch.Tensor],
                    tok_seq: torch.Tensor, tok_pos: torch.Tensor, tables: torch.Tensor, scale: float, chunk: int,
-                   out_dtype: torch.dtype, atoms: Optional[torch.Tensor] = None, n_long: int = 0) -> torch.Tensor:
+                   out_dtype: torch.dtype, atoms: Optional[torch.Tensor] = None, n_long: int = 0, window: int = 0,
+                   value_cols: int = 0, value_col0: int = 0) -> torch.Tensor:
     """Softmax attention of each token (fp32 ``q`` ``[T, Hq, d]``) over the cached keys ``lo..pos`` of its sequence,
-    ``lo`` = first position of the token's chunk of ``chunk`` positions (0: plain causal).  ``sink`` (fp32 ``[Hq]``)
-    adds ``exp(sink[h])`` to the denominator.  Returns ``[T, Hq * dv]``.
+    ``lo`` = first position of the token's chunk of ``chunk`` positions, or ``pos - window + 1`` (not below 0) for a
+    sliding ``window``, or 0 (both 0: plain causal).  ``sink`` (fp32 ``[Hq]``) adds ``exp(sink[h])`` to the
+    denominator.  Returns ``[T, Hq * dv]``.
+
+    ``value_cols = dv > 0``: the values are the ``dv`` columns of the key rows that start at ``value_col0`` (one key
+    head; ``vcache`` is not read) -- attention in a latent space where a key is ``[latent | extra]`` and its value the
+    latent itself.
 
     With the batch's attention ``atoms`` (longest first) of which the first ``n_long`` hold more than
     :data:`SHORT_ATOM` queries, those run the tiled kernel (64 queries per CTA, K/V tiles shared by them) and the rest
     one warp per (query, head); without atoms every token takes the latter."""
     T, Hq, d = q.shape
-    bs, G, dv = kcache.shape[1], kcache.shape[2], vcache.shape[3]
+    bs, G = kcache.shape[1], kcache.shape[2]
+    if value_cols > 0:
+        if G != 1:
+            raise ValueError("values taken from the key rows need a single key head")
+        dv, vsrc, v_pitch = int(value_cols), kcache, d
+    else:
+        dv, vsrc, v_pitch = vcache.shape[3], vcache, 0
     if q.is_cuda:
-        if kcache.dtype != out_dtype or vcache.dtype != out_dtype:
+        if kcache.dtype != out_dtype or vsrc.dtype != out_dtype:
             raise ValueError("the caches and the output share one activation dtype")
         out = torch.empty(T, Hq * dv, dtype=out_dtype, device=q.device)
+        vptr = vsrc.data_ptr() + (value_col0 * vsrc.element_size() if value_cols > 0 else 0)
+        if value_cols > 0 and value_col0 % 8:
+            raise ValueError("value columns start at a multiple of 8")
         if atoms is not None and n_long > 0 and tiles_supported(d, dv):
-            _lib.call("sxb_sink_attention_atoms", q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), _lib.ptr(sink),
+            _lib.call("sxb_sink_attention_atoms", q.data_ptr(), kcache.data_ptr(), vptr, _lib.ptr(sink),
                       out.data_ptr(), atoms.data_ptr(), atoms.shape[0], int(n_long), tables.data_ptr(), tables.shape[1],
-                      bs, Hq, G, d, dv, float(scale), int(chunk), _lib.dtype_code(out_dtype), _lib.stream_ptr())
+                      bs, Hq, G, d, dv, float(scale), int(chunk), int(window), 0, v_pitch, _lib.dtype_code(out_dtype),
+                      _lib.stream_ptr())
             return out
-        _lib.call("sxb_sink_attention", q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), _lib.ptr(sink),
+        _lib.call("sxb_sink_attention", q.data_ptr(), kcache.data_ptr(), vptr, _lib.ptr(sink),
                   out.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), tables.data_ptr(), T, tables.shape[1], bs, Hq,
-                  G, d, dv, float(scale), int(chunk), _lib.dtype_code(out_dtype), _lib.stream_ptr())
+                  G, d, dv, float(scale), int(chunk), int(window), 0, v_pitch, _lib.dtype_code(out_dtype),
+                  _lib.stream_ptr())
         return out
     out = torch.empty(T, Hq, dv, dtype=torch.float32)
     rep = Hq // G
     for t in range(T):
         pos = int(tok_pos[t])
-        lo = (pos // chunk) * chunk if chunk > 0 else 0
+        lo = (pos // chunk) * chunk if chunk > 0 else (max(0, pos - window + 1) if window > 0 else 0)
         js = torch.arange(lo, pos + 1)
         page = tables[int(tok_seq[t]), (js // bs)].long()
         k = kcache[page, js % bs].float().repeat_interleave(rep, dim=1)      # [n, Hq, d]
-        v = vcache[page, js % bs].float().repeat_interleave(rep, dim=1)
+        if value_cols > 0:
+            v = k[:, :, value_col0: value_col0 + dv]
+        else:
+            v = vcache[page, js % bs].float().repeat_interleave(rep, dim=1)
         s = torch.einsum("hd,nhd->hn", q[t], k) * scale
         if sink is not None:
             s = torch.cat([s, sink.float()[:, None]], dim=1)
@@ -315,3 +347,199 @@ def gated_act_rows(x: torch.Tensor, act: str = "gelu") -> torch.Tensor:
     a = {"gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "silu": torch.nn.functional.silu,
          "relu": torch.relu, "identity": lambda t: t}[act](g)
     return (a * u).to(x.dtype)
+
+
+def bias_act_rows(x: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> torch.Tensor:
+    """``act(x + bias)`` for rows of any width, bf16 or fp32; ``relu_sq`` is ``relu(z) ** 2``."""
+    T, Fw = x.shape
+    if x.is_cuda:
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        _lib.call("sxb_bias_act_rows", x.data_ptr(), _lib.ptr(bias), out.data_ptr(), T, Fw, _ACTS[act], _dt(x),
+                  _lib.stream_ptr())
+        return out
+    z = x.float() + (bias.float() if bias is not None else 0.0)
+    a = {"gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "silu": torch.nn.functional.silu,
+         "relu": torch.relu, "identity": lambda t: t, "relu_sq": lambda t: torch.relu(t) ** 2}[act](z)
+    return a.to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ post-norm layers
+def conv_residual(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, seq_info: torch.Tensor, tok_seq: torch.Tensor,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """``x + filter(x)`` over the fp32 rows ``x`` ``[T, C]`` of a ragged batch: ``filter(x)[t] = sum_j w[:, j] x[t - taps +
+    1 + j]`` per channel (``w`` ``[C, taps]``), earlier rows of a sequence from ``state`` fp32 ``[slots, taps-1, C]``,
+    rows before its start zero.  Returns ``out_dtype`` ``[T, C]``; call :func:`conv_state_update` on ``x`` afterwards."""
+    T, C = x.shape
+    taps = w.shape[1]
+    if x.is_cuda:
+        out = torch.empty(T, C, dtype=out_dtype, device=x.device)
+        if w.dtype != out_dtype:
+            raise ValueError("the filter is stored in the activation dtype")
+        _lib.call("sxb_conv_residual", x.data_ptr(), w.data_ptr(), state.data_ptr(), seq_info.data_ptr(),
+                  tok_seq.data_ptr(), out.data_ptr(), T, C, taps, _lib.dtype_code(out_dtype), _lib.stream_ptr())
+        return out
+    out = torch.empty(T, C, dtype=torch.float32)
+    wf = w.float()
+    for first, n, seen, slot in seq_info.tolist():
+        hist = state[slot].float() if seen > 0 else torch.zeros(taps - 1, C)
+        if 0 < seen < taps - 1:
+            hist = hist.clone()
+            hist[: taps - 1 - seen] = 0
+        full = torch.cat([hist, x[first: first + n]], dim=0)
+        acc = torch.zeros(n, C)
+        for j in range(taps):
+            acc += wf[:, j] * full[j: j + n]
+        out[first: first + n] = x[first: first + n] + acc
+    return out.to(out_dtype)
+
+
+def post_norm_mix(x_in: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, ls: torch.Tensor, x_out: torch.Tensor,
+                  eps: float, stack: Optional[torch.Tensor] = None, n_prev: int = 0,
+                  mixw: Optional[torch.Tensor] = None, mix_out: Optional[torch.Tensor] = None) -> None:
+    """``x_out = x_in + ls * (y / rms(y) * gain)`` on fp32 rows (``gain`` fp32 ``[1]``, ``ls`` fp32 ``[W]``; ``x_out`` may
+    be ``x_in``).  With ``mix_out``: ``mix_out = sum_{j < n_prev} mixw[j] * stack[j] + mixw[n_prev] * x_out`` (``stack``
+    fp32 ``[>= n_prev, T, W]``, ``mixw`` fp32)."""
+    T, W = x_in.shape
+    if x_in.is_cuda:
+        stride = stack.stride(0) if stack is not None else 0
+        _lib.call("sxb_post_norm_mix", x_in.data_ptr(), y.data_ptr(), gain.data_ptr(), ls.data_ptr(), x_out.data_ptr(),
+                  _lib.ptr(stack), stride, int(n_prev), _lib.ptr(mixw), _lib.ptr(mix_out), T, W, float(eps), _dt(y),
+                  _lib.stream_ptr())
+        return
+    v = x_in + _rms(y.float(), eps) * gain.float() * ls.float()
+    x_out.copy_(v)
+    if mix_out is not None:
+        m = torch.zeros_like(v)
+        for j in range(n_prev):
+            m += mixw[j] * stack[j]
+        mix_out.copy_(m + mixw[n_prev] * v)
+
+
+def rms_scale_rows(x: torch.Tensor, rows: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """``x[rows] / rms * gain`` (one fp32 gain for all channels) of fp32 rows, in ``out_dtype``."""
+    n = x.shape[0] if rows is None else rows.numel()
+    W = x.shape[1]
+    if x.is_cuda:
+        out = torch.empty(n, W, dtype=out_dtype, device=x.device)
+        _lib.call("sxb_rms_scale_rows", x.data_ptr(), _lib.ptr(rows), gain.data_ptr(), out.data_ptr(), n, W, float(eps),
+                  _lib.dtype_code(out_dtype), _lib.stream_ptr())
+        return out
+    sel = x if rows is None else x.index_select(0, rows.long())
+    return (_rms(sel, eps) * gain.float()).to(out_dtype)
+
+
+def rms_norm_slice(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm with weight over the columns of ``x`` (a column slice of a wider matrix is fine), computed in fp32."""
+    T, n = x.shape
+    if x.is_cuda:
+        out = torch.empty(T, n, dtype=x.dtype, device=x.device)
+        _lib.call("sxb_rms_norm_slice", _rows(x).data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), T, n, float(eps),
+                  _dt(x), _lib.stream_ptr())
+        return out
+    return (_rms(x.float(), eps) * w.float()).to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ latent attention
+def _rope_pairs(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """Rotate the pairs (2i, 2i+1), i < len(inv_freq), of the last axis of fp32 ``x`` ``[T, ..., n]`` by ``pos * inv_freq``."""
+    nd = 2 * inv_freq.numel()
+    ang = pos.float()[:, None] * inv_freq.float()[None, :]
+    shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (nd // 2,)
+    cs, sn = ang.cos().view(shape), ang.sin().view(shape)
+    out = x.clone()
+    u, v = x[..., 0:nd:2], x[..., 1:nd:2]
+    out[..., 0:nd:2] = u * cs - v * sn
+    out[..., 1:nd:2] = v * cs + u * sn
+    return out
+
+
+def latent_qk_prepare(q: torch.Tensor, q_abs: torch.Tensor, kv: torch.Tensor, w_norm: torch.Tensor,
+                      inv_freq: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
+                      tables: torch.Tensor, H: int, dim: int, rot: int, eps: float) -> torch.Tensor:
+    """Latent attention, per token.  ``kv`` ``[T, r + rot]``: ``cache[page, offset, 0] = [kv[:r] / rms * w_norm |
+    rope(kv[r:])]`` (``cache`` ``[pages, block, 1, r + rot]``).  ``q`` ``[T, H * (dim + rot)]`` (heads laid out
+    ``[dim unrotated | rot rotated]``) and ``q_abs`` ``[T, H, r]`` (any strides with unit inner stride; the unrotated
+    part of every query head carried through the key up-projection): returns fp32 ``[T, H, r + rot] = [q_abs |
+    rope(q[..., dim:])]``.  ``rope`` turns the pairs ``(2i, 2i+1)``, ``i < len(inv_freq)``, by ``pos * inv_freq[i]``."""
+    T = q.shape[0]
+    r = kv.shape[1] - rot
+    bs = cache.shape[1]
+    if q.is_cuda:
+        out = torch.empty(T, H, r + rot, dtype=torch.float32, device=q.device)
+        _lib.call("sxb_latent_qk_prepare", _rows(q).data_ptr(), q.stride(0), _rows(q_abs).data_ptr(), q_abs.stride(0),
+                  q_abs.stride(1), _rows(kv).data_ptr(), kv.stride(0), w_norm.data_ptr(), inv_freq.data_ptr(),
+                  out.data_ptr(), cache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), tables.data_ptr(), T,
+                  tables.shape[1], bs, H, dim, rot, r, 2 * inv_freq.numel(), float(eps), _dt(q), _lib.stream_ptr())
+        return out
+    c = (_rms(kv[:, :r].float(), eps) * w_norm.float()).to(cache.dtype)
+    kr = _rope_pairs(kv[:, r:].float(), tok_pos, inv_freq).to(cache.dtype)
+    page = tables[tok_seq.long(), (tok_pos // bs).long()].long()
+    off = (tok_pos % bs).long()
+    cache[page, off, 0] = torch.cat([c, kr], dim=1)
+    qr = _rope_pairs(q.reshape(T, H, dim + rot)[:, :, dim:].float(), tok_pos, inv_freq)
+    return torch.cat([q_abs.float(), qr], dim=2).contiguous()
+
+
+# ------------------------------------------------------------------------------------------------ matrix-memory LSTM
+def mlstm_prepare(proj: torch.Tensor, H: int, n: int, dv: int, qscale: float) -> torch.Tensor:
+    """fp32 ``[T, 2 H n + H (dv + 1)] = [q * qscale | k | per head (v, 1)]`` from projection rows that start with
+    ``q (H n) | k (H n) | v (H dv)``; the constant channel makes the recurrence carry the normaliser ``sum decay.. k``."""
+    T = proj.shape[0]
+    if proj.is_cuda:
+        buf = torch.empty(T, 2 * H * n + H * (dv + 1), dtype=torch.float32, device=proj.device)
+        _lib.call("sxb_mlstm_prepare", _rows(proj).data_ptr(), proj.stride(0), buf.data_ptr(), T, H, n, dv, float(qscale),
+                  _dt(proj), _lib.stream_ptr())
+        return buf
+    q = proj[:, : H * n].float() * qscale
+    k = proj[:, H * n: 2 * H * n].float()
+    v = proj[:, 2 * H * n: 2 * H * n + H * dv].float().reshape(T, H, dv)
+    v1 = torch.cat([v, torch.ones(T, H, 1)], dim=2).reshape(T, H * (dv + 1))
+    return torch.cat([q, k, v1], dim=1)
+
+
+def mlstm_gate_scan(raw_i: torch.Tensor, raw_f: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+                    mstate: torch.Tensor, seq_info: torch.Tensor):
+    """Exponential gating with a running maximum.  ``raw_i`` / ``raw_f`` ``[T, H]`` (column slices of one matrix),
+    biases fp32 ``[H]``: ``i = cap tanh((raw_i + b_i) / cap)``, ``f = logsigmoid(cap tanh((raw_f + b_f) / cap))``,
+    ``m_t = max(f_t + m_(t-1), i_t)`` with ``m`` from ``mstate`` fp32 ``[slots, H]`` (0 for a sequence that has seen no
+    token; written back).  Returns fp32 ``[T, H]`` ``(decay = exp(f + m_(t-1) - m_t), beta = exp(i - m_t), m_t)``."""
+    T, H = raw_i.shape
+    if raw_i.is_cuda:
+        if raw_i.stride(0) != raw_f.stride(0):
+            raise ValueError("raw_i and raw_f must share their row pitch")
+        decay = torch.empty(T, H, dtype=torch.float32, device=raw_i.device)
+        beta, mt = torch.empty_like(decay), torch.empty_like(decay)
+        _lib.call("sxb_mlstm_gate_scan", _rows(raw_i).data_ptr(), _rows(raw_f).data_ptr(), raw_i.stride(0),
+                  bias_i.data_ptr(), bias_f.data_ptr(), float(cap), mstate.data_ptr(), decay.data_ptr(), beta.data_ptr(),
+                  mt.data_ptr(), seq_info.data_ptr(), seq_info.shape[0], H, _dt(raw_i), _lib.stream_ptr())
+        return decay, beta, mt
+    ig = cap * torch.tanh((raw_i.float() + bias_i.float()) / cap)
+    fg = torch.nn.functional.logsigmoid(cap * torch.tanh((raw_f.float() + bias_f.float()) / cap))
+    decay, beta, mt = torch.empty(T, H), torch.empty(T, H), torch.empty(T, H)
+    for first, rows, seen, slot in seq_info.tolist():
+        m = mstate[slot].clone() if seen > 0 else torch.zeros(H)
+        for t in range(first, first + rows):
+            mn = torch.maximum(fg[t] + m, ig[t])
+            decay[t], beta[t], mt[t] = torch.exp(fg[t] + m - mn), torch.exp(ig[t] - mn), mn
+            m = mn
+        mstate[slot] = m
+    return decay, beta, mt
+
+
+def mlstm_output(o: torch.Tensor, mt: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, H: int, dv: int, eps: float,
+                 out_dtype: torch.dtype) -> torch.Tensor:
+    """``o`` fp32 ``[T, H (dv + 1)]`` (read-out of the values and, last per head, of the normaliser): per head
+    ``h = o[:dv] / (max(|o[dv]|, exp(-m_t)) + 1e-6)``, then ``h / rms(h) * w * sigmoid(gate)`` in ``out_dtype``
+    ``[T, H dv]``."""
+    T = o.shape[0]
+    if o.is_cuda:
+        out = torch.empty(T, H * dv, dtype=out_dtype, device=o.device)
+        _lib.call("sxb_mlstm_output", o.data_ptr(), mt.data_ptr(), _rows(gate).data_ptr(), gate.stride(0), w.data_ptr(),
+                  out.data_ptr(), T, H, dv, float(eps), _lib.dtype_code(out_dtype), _lib.stream_ptr())
+        return out
+    oo = o.reshape(T, H, dv + 1)
+    den = torch.maximum(oo[:, :, dv].abs(), torch.exp(-mt)) + 1e-6
+    h = _rms(oo[:, :, :dv] / den[:, :, None], eps).reshape(T, H * dv)
+    return (h * w.float() * torch.sigmoid(gate.float())).to(out_dtype)

@@ -1,10 +1,17 @@
-"""Ragged-batch model for hybrid layer stacks: every layer names its own token mixer — attention over the paged cache, a
-gated-delta-rule recurrence or a state-space-duality recurrence — and may or may not have a feed-forward; a span of
-layers can be executed several times in a row with the same weights, every execution with its own cache or state.
+"""Ragged-batch model for hybrid layer stacks: every layer names its own token mixer — attention over the paged cache
+(per-head keys and values, or one latent vector per token), a gated-delta-rule, state-space-duality or matrix-memory
+LSTM recurrence — and may or may not have a feed-forward (gated, biased, or a mixture of experts); a span of layers can
+be executed several times in a row with the same weights, every execution with its own cache or state.
 
 The stack is data (:class:`HybridSpec`), as :class:`~.inference_transformer_base.ArchSpec` is for the uniform
 transformer family; per-architecture policies (``fomalix/policy.py``) fill it from a checkpoint's configuration and fuse
 the checkpoint's tensors into the projection layouts the mixer modules declare.
+
+Two layer forms (``HybridSpec.block_form``).  ``"sandwich"``: ``x += post_norm(sublayer(pre_norm(x)))``.
+``"post_scaled"``: ``x += scale (.) post_norm(sublayer(x + conv(x)))`` -- no pre-norm, a post-norm with one gain, a
+per-channel scale, a short causal filter with a skip path in front of every sublayer (its last inputs are state of the
+sequence), and optionally the stream handed to the next layer is a learned mixture of the embedding and of all
+layers' results so far (``depth_mix``).
 
 Numerics: the residual stream, norms, softmax, recurrences and their gates are fp32; projections, short convolutions'
 inputs, the KV cache and the sublayer outputs use ``spec.dtype`` (bf16 when serving; fp32 evaluates everything in
@@ -24,8 +31,8 @@ from ..config_v2 import RaggedInferenceEngineConfig
 from ..inference_utils import ActivationType, DtypeEnum, NormTypeEnum, ceil_div
 from ..kernels import mixer_ops as M
 from ..modules import heuristics
-from ..modules.configs import (DSEmbeddingsConfig, DSLinearConfig, DSNormConfig, DSRecurrentMixerConfig,
-                               DSSelfAttentionConfig, MaskingType, PositionalEmbeddingType)
+from ..modules.configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSRecurrentMixerConfig,
+                               DSSelfAttentionConfig, MaskingType, PositionalEmbeddingType, RotateHalfConfig)
 from ..ragged.kv_cache import KVCacheConfig
 from ..ragged.state_pool import StatePoolConfig
 from .inference_transformer_base import DSInferenceModelBase, LayerWeights
@@ -33,7 +40,7 @@ from .inference_transformer_base import DSInferenceModelBase, LayerWeights
 
 @dataclass
 class HybridLayerSpec:
-    kind: str                                   # "attention" | "delta" | "ssd"
+    kind: str                                   # "attention" | "latent_attention" | "delta" | "ssd" | "mlstm"
     n_heads: int
     n_heads_kv: int                             # key/value heads (attention), key/query heads (delta), groups (ssd)
     key_dim: int                                # query/key head size, or state size per group (ssd)
@@ -47,6 +54,18 @@ class HybridLayerSpec:
     norm_groups: int = 1
     ff_dim: int = 0                             # 0: the layer has no feed-forward
     ff_activation: str = "gelu"
+    ff_kind: str = "gated"                      # "gated": down(act(gate) * up); "biased": down(act(up + b)) + b; "moe"
+    n_experts: int = 0                          # moe: experts are gated feed-forwards of ff_dim channels
+    top_k: int = 1
+    moe_score: str = "softmax"
+    moe_weight_input: bool = False
+    window: int = 0                             # attention: > 0 = the query and the window - 1 positions before it
+    q_rank: int = 0                             # latent attention: query latent, key/value latent, rotated channels
+    kv_rank: int = 0
+    rot_dim: int = 0
+    rot_dims: int = 0                           # how many of the rot_dim channels turn (in interleaved pairs)
+    rot_base: float = 10000.0
+    gate_cap: float = 0.0                       # mlstm
 
 
 @dataclass
@@ -62,6 +81,9 @@ class HybridSpec:
     loop_times: int = 1
     dtype: torch.dtype = torch.bfloat16
     max_seq_len: int = 1 << 20
+    block_form: str = "sandwich"                # "sandwich" | "post_scaled"
+    input_conv_taps: int = 0                    # post_scaled: taps of the filter in front of every sublayer
+    depth_mix: bool = False                     # post_scaled: every layer hands on a mixture of all results so far
 
     def runs(self) -> List[Tuple[int, bool]]:
         """[(layer index, whether a repeated pass starts here)] in execution order: the layers before the span once,
@@ -106,7 +128,8 @@ class DSHybridModel(DSInferenceModelBase):
         self._runs = spec.runs()
         # which cache / state entries every execution of a layer uses
         self._cache_of_run: Dict[int, int] = {}
-        self._state_of_run: Dict[int, Tuple[int, int]] = {}
+        self._state_of_run: Dict[int, Tuple[int, ...]] = {}
+        self._conv_of_run: Dict[int, Tuple[int, int]] = {}
         self._build_modules()
 
     # ------------------------------------------------------------------------------------------ construction
@@ -116,15 +139,41 @@ class DSHybridModel(DSInferenceModelBase):
         dt, mt = DtypeEnum(s.dtype), sm.max_ragged_batch_size
         self.embed = heuristics.instantiate_embed(DSEmbeddingsConfig(
             max_tokens=mt, residual_dtype=DtypeEnum.fp32, embedding_dim=s.model_dim, scale=s.embed_scale,
-            sinusoid_base=s.sinusoid_base), ec)
+            sinusoid_base=s.sinusoid_base, widen_to_residual=True), ec)
         self.norm = heuristics.instantiate_sandwich_norm(DSNormConfig(
             max_tokens=mt, type=NormTypeEnum.RMSNorm, channels=s.model_dim, residual_dtype=DtypeEnum.fp32,
             input_dtype=dt, output_dtype=dt, eps=s.norm_eps), ec)
         self.linear = heuristics.instantiate_linear(DSLinearConfig(
             max_tokens=mt, in_channels=s.model_dim, out_channels=s.model_dim, input_dtype=dt, output_dtype=dt), ec)
-        self.mixers = []
+        if s.block_form == "post_scaled":
+            self.post_norm = heuristics.instantiate_scaled_post_norm(DSNormConfig(
+                max_tokens=mt, type=NormTypeEnum.RMSNorm, channels=s.model_dim, residual_dtype=DtypeEnum.fp32,
+                input_dtype=dt, output_dtype=dt, eps=s.norm_eps), ec)
+        elif s.block_form != "sandwich":
+            raise ValueError(f"unknown block form {s.block_form!r}")
+        self.mixers, self.moes = [], []
         for L in s.layers:
-            if L.kind == "attention":
+            moe = None
+            if L.ff_dim > 0 and L.ff_kind == "moe":
+                moe = heuristics.instantiate_moe(DSMoEConfig(
+                    max_tokens=mt, model_dim=s.model_dim, intermediate_features=L.ff_dim, n_experts=L.n_experts,
+                    top_k=L.top_k, input_dtype=dt, output_dtype=dt,
+                    activation={"silu": ActivationType.SiGLU, "gelu": ActivationType.GEGLU,
+                                "relu": ActivationType.ReGLU}[L.ff_activation],
+                    score_function=L.moe_score, weight_input=L.moe_weight_input, router_dtype=DtypeEnum.fp32), ec)
+            self.moes.append(moe)
+            if L.kind == "latent_attention":
+                mod = heuristics.instantiate_attention(DSSelfAttentionConfig(
+                    max_tokens=mt, n_heads_q=L.n_heads, n_heads_kv=1, head_size=L.key_dim, v_head_size=L.value_dim,
+                    max_sequences=sm.max_ragged_sequence_count, scale_factor=L.attn_scale, input_dtype=dt,
+                    output_dtype=dt,
+                    masking_type=MaskingType.sliding_window if L.window > 0 else MaskingType.causal,
+                    masking_args={"size": L.window} if L.window > 0 else {},
+                    positional_embedding_type=(PositionalEmbeddingType.rotate_every_other if L.rot_dims > 0
+                                               else PositionalEmbeddingType.none),
+                    positional_embedding_config=RotateHalfConfig(theta_base=L.rot_base, rotate_dim=L.rot_dims),
+                    qk_norm_eps=s.norm_eps, sink=L.sink, kv_latent_dim=L.kv_rank, rope_head_dim=L.rot_dim), ec)
+            elif L.kind == "attention":
                 mod = heuristics.instantiate_attention(DSSelfAttentionConfig(
                     max_tokens=mt, n_heads_q=L.n_heads, n_heads_kv=L.n_heads_kv, head_size=L.key_dim,
                     v_head_size=L.value_dim, max_sequences=sm.max_ragged_sequence_count, scale_factor=L.attn_scale,
@@ -137,7 +186,7 @@ class DSHybridModel(DSInferenceModelBase):
                 mod = heuristics.instantiate_recurrent_mixer(DSRecurrentMixerConfig(
                     max_tokens=mt, kind=L.kind, model_dim=s.model_dim, n_heads=L.n_heads, n_heads_kv=L.n_heads_kv,
                     key_dim=L.key_dim, value_dim=L.value_dim, conv_taps=L.conv_taps, norm_groups=L.norm_groups,
-                    eps=s.norm_eps, max_sequences=sm.max_ragged_sequence_count, input_dtype=dt, output_dtype=dt), ec)
+                    gate_cap=L.gate_cap, eps=s.norm_eps, max_sequences=sm.max_ragged_sequence_count, input_dtype=dt, output_dtype=dt), ec)
             self.mixers.append(mod)
         n_cache = 0
         self._state_cfg = StatePoolConfig()
@@ -148,10 +197,20 @@ class DSHybridModel(DSInferenceModelBase):
                 self._cache_of_run[r] = n_cache
                 shapes.append((L.n_heads_kv, L.key_dim, L.value_dim))
                 n_cache += 1
+            elif L.kind == "latent_attention":
+                self._cache_of_run[r] = n_cache
+                shapes.append((1, self.mixers[li].cache_row, 0))        # latent | rotated key part; no value tensor
+                n_cache += 1
             else:
-                (conv_shape, conv_dt), (mat_shape, mat_dt) = self.mixers[li].state_shapes()
-                self._state_of_run[r] = (self._state_cfg.add(conv_shape, conv_dt), self._state_cfg.add(mat_shape, mat_dt))
+                self._state_of_run[r] = tuple(self._state_cfg.add(shape, sdt)
+                                              for shape, sdt in self.mixers[li].state_shapes())
+            if s.block_form == "post_scaled":
+                # the last taps - 1 inputs of the filter in front of the mixer and of the one in front of the feed-forward
+                keep = (max(s.input_conv_taps, 1) - 1, s.model_dim)
+                self._conv_of_run[r] = (self._state_cfg.add(keep, torch.float32),
+                                        self._state_cfg.add(keep, torch.float32) if L.ff_dim > 0 else -1)
         self._cache_shapes = tuple(shapes)
+        self._stack = None
 
     # ------------------------------------------------------------------------------------------ properties
     @property
@@ -196,7 +255,12 @@ class DSHybridModel(DSInferenceModelBase):
         """Chunk-local layers could return the pages before the current chunk; every page is kept."""
 
     # ------------------------------------------------------------------------------------------ forward
-    def _feed_forward(self, L: HybridLayerSpec, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+    def _feed_forward(self, L: HybridLayerSpec, lw: LayerWeights, x: torch.Tensor, li: int = -1) -> torch.Tensor:
+        if L.ff_kind == "moe":
+            return self.moes[li](x, lw.moe_gate, lw.moe_w1, lw.moe_w2)
+        if L.ff_kind == "biased":
+            h = M.bias_act_rows(self.linear(x, lw.w_up), lw.b_up, L.ff_activation)
+            return F.linear(h, lw.w_down, lw.b_down)
         h = self.linear(x, lw.w_gate_up)
         if h.is_cuda and h.dtype == torch.bfloat16 and L.ff_dim % 8 == 0:
             h = F.gated_act(h, L.ff_activation)
@@ -209,14 +273,64 @@ class DSHybridModel(DSInferenceModelBase):
         proj = self.linear(x, lw.w_in)
         if L.kind == "attention":
             ctx = mod(proj, sm.get_cache(self._cache_of_run[r]), batch, None, lw.b_in, lw.sink)
+        elif L.kind == "latent_attention":
+            ctx = mod(proj, sm.get_cache(self._cache_of_run[r]), batch, None, lw)
         else:
-            ci, si = self._state_of_run[r]
-            ctx = mod(proj, lw, (sm.get_state(ci), sm.get_state(si)), batch)
+            ctx = mod(proj, lw, tuple(sm.get_state(e) for e in self._state_of_run[r]), batch)
         return self.linear(ctx, lw.wo)
+
+    def _filtered(self, x: torch.Tensor, w: torch.Tensor, entry: int, batch) -> torch.Tensor:
+        """What a sublayer of a post-scaled layer reads: ``x + filter(x)`` in the activation dtype; the sequence's
+        carried inputs move on by this batch's rows."""
+        state = self.state_manager.get_state(entry)
+        h = M.conv_residual(x, w, state, batch.seq_info(), batch.token_to_seq(), self.spec.dtype)
+        M.conv_state_update(x, state, batch.seq_info())
+        return h
+
+    @torch.no_grad()
+    def _forward_post_scaled(self, batch) -> torch.Tensor:
+        """Layers ``x <- x + ls1 (.) norm1(mixer(x + conv1(x)))``, ``x <- x + ls2 (.) norm2(ff(x + conv2(x)))``; with
+        ``depth_mix`` layer ``i`` hands on ``sum_j mix[j] X_j`` over the embedding ``X_0`` and the results ``X_1 ..
+        X_(i+1)`` of the layers so far, which are kept as a stack of fp32 streams for the length of the forward."""
+        W, s = self.weights, self.spec
+        T = batch.current_tokens
+        n_runs = len(self._runs)
+        x = self.embed(batch, W["embed"])
+        if s.depth_mix:
+            if self._stack is None or self._stack.shape[1] < T:
+                self._stack = torch.empty(n_runs + 1, max(T, 1), s.model_dim, dtype=torch.float32, device=x.device)
+            stack = self._stack[:, :T]
+            stack[0].copy_(x)
+        for r, (li, _) in enumerate(self._runs):
+            lw, L = W["layers"][li], s.layers[li]
+            c1, c2 = self._conv_of_run[r]
+            y = self._mixer(r, li, lw, self._filtered(x, lw.conv1, c1, batch), batch)
+            last = L.ff_dim == 0
+            mid = torch.empty_like(x)
+
+            def close(x_in, y, gain, scale, final):
+                if not final:
+                    return self.post_norm(x_in, y, gain, None, scale, mid)
+                if not s.depth_mix:
+                    return self.post_norm(x_in, y, gain, None, scale, mid)
+                nxt = torch.empty_like(x_in)
+                self.post_norm(x_in, y, gain, None, scale, stack[r + 1], (stack, r + 1, lw.depth_mix, nxt))
+                return nxt
+            x = close(x, y, lw.norm1, lw.ls1, last)
+            if not last:
+                y = self._feed_forward(L, lw, self._filtered(x, lw.conv2, c2, batch), li)
+                x = close(x, y, lw.norm2, lw.ls2, True)
+        rows = batch.last_token_index()
+        if rows.numel() == 0:               # a step that only advances caches and states
+            return torch.empty(0, s.vocab_size, dtype=torch.float32, device=x.device)
+        h = M.rms_scale_rows(x, rows, W["final_norm_w"], s.norm_eps, s.dtype)
+        return self.linear(h, W["unembed"])[:, : s.vocab_size].float()
 
     @torch.no_grad()
     def forward(self, batch) -> torch.Tensor:
         W, s = self.weights, self.spec
+        if s.block_form == "post_scaled":
+            return self._forward_post_scaled(batch)
         resid = self.embed(batch, W["embed"])
         first = resid.clone() if any(again for _, again in self._runs) else None
         y = post = None                     # output of the last sublayer and its post-norm weight, not yet added
@@ -226,7 +340,7 @@ class DSHybridModel(DSInferenceModelBase):
             y, post = self._mixer(r, li, lw, x, batch), lw.norm1b
             if L.ff_dim > 0:
                 _, x = self.norm(resid, y, lw.norm2, None, post, None)
-                y, post = self._feed_forward(L, lw, x), lw.norm2b
+                y, post = self._feed_forward(L, lw, x, li), lw.norm2b
         rows = batch.last_token_index().long()
         if rows.numel() == 0:               # a step that only advances caches and states
             return torch.empty(0, s.vocab_size, dtype=torch.float32, device=resid.device)

@@ -27,6 +27,7 @@ class MaskingType(Enum):
     symmetric = "symmetric"
     asymmetric = "asymmetric"
     chunked = "chunked"      # causal inside aligned chunks of ``masking_args["size"]`` positions, nothing across chunks
+    sliding_window = "sliding_window"   # causal over the query and the ``masking_args["size"] - 1`` positions before it
 
 
 class DSSelfAttentionConfig(DSModuleConfig):
@@ -45,6 +46,12 @@ class DSSelfAttentionConfig(DSModuleConfig):
     qk_unit_rms: bool = False             # divide every query / key head by its root mean square (no weight)
     qk_norm_eps: float = 1e-5
     sink: bool = False                    # one learned logit per head joins the softmax denominator
+    # Latent attention: keys and values are up-projections of one normalised latent vector of ``kv_latent_dim`` channels
+    # per token, and every query / key head has ``rope_head_dim`` further channels that carry the rotation (the key's are
+    # shared by all heads).  ``head_size`` is then the unrotated query / key head size and the cache holds
+    # ``kv_latent_dim + rope_head_dim`` channels per token.
+    kv_latent_dim: Optional[int] = None
+    rope_head_dim: int = 0
 
 
 class DSEmbeddingsConfig(DSModuleConfig):
@@ -56,6 +63,7 @@ class DSEmbeddingsConfig(DSModuleConfig):
     output_normalization: Optional[NormTypeEnum] = None
     scale: float = 1.0                    # multiplies the token rows
     sinusoid_base: Optional[float] = None  # adds interleaved sin / cos of pos * base^(-2i/dim) when set
+    widen_to_residual: bool = False       # the stream is fp32 whatever the table's dtype: rows are converted on the way
 
 
 class DSLinearConfig(DSModuleConfig):
@@ -75,6 +83,9 @@ class DSMoEConfig(DSModuleConfig):
     output_dtype: DtypeEnum = DtypeEnum.bf16
     activation: ActivationType = ActivationType.IDENTITY
     normalize_scores: bool = False
+    score_function: str = "softmax"       # "softmax" over all experts, or "sigmoid" of every expert's own logit
+    weight_input: bool = False            # the routing weight scales the expert's input instead of its output
+    router_dtype: Optional[DtypeEnum] = None    # dtype of the router product (None: the activation dtype)
 
 
 class DSNormConfig(DSModuleConfig):
@@ -100,15 +111,18 @@ class DSRecurrentMixerConfig(DSModuleConfig):
 
     ``kind`` ``"delta"``: gated delta rule (keys / queries of ``key_dim`` channels shared by ``n_heads // n_heads_kv``
     value heads, short convolutions on q, k, v).  ``"ssd"``: state-space duality (B / C of ``key_dim`` = state size per
-    group, a convolution over x | B | C, a skip term and a gated group norm)."""
+    group, a convolution over x | B | C, a skip term and a gated group norm).  ``"mlstm"``: matrix-memory LSTM
+    (exponential input gate, sigmoid forget gate in log space, both capped by ``gate_cap``, a running maximum that
+    keeps the exponentials in range, a normaliser state, per-head unit-RMS and a sigmoid output gate; no convolution)."""
     kind: str
     model_dim: int
     n_heads: int
     n_heads_kv: int                       # key/query heads (delta) or B/C groups (ssd)
     key_dim: int
     value_dim: int
-    conv_taps: int
+    conv_taps: int = 1
     norm_groups: int = 1
+    gate_cap: float = 0.0                 # mlstm: gate pre-activations pass cap * tanh(x / cap)
     eps: float = 1e-5
     unit_norm_eps: float = 1e-6
     max_sequences: int = 1

@@ -15,6 +15,9 @@ from .module_registry import ConfigBundle
 
 def instantiate_attention(attention_config: DSSelfAttentionConfig,
                           engine_config: RaggedInferenceEngineConfig) -> DSSelfAttentionBase:
+    if attention_config.kv_latent_dim is not None:
+        return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="latent_sink_attention",
+                                                                       config=attention_config))
     name = "dense_blocked_attention"
     if not DSSelfAttentionRegistry.registry[name].supports_config(attention_config):
         name = "sink_chunked_attention"       # chunk-local mask, sink logit, q/k unit norm or narrower value heads
@@ -22,7 +25,8 @@ def instantiate_attention(attention_config: DSSelfAttentionConfig,
 
 
 def instantiate_embed(embed_config: DSEmbeddingsConfig, engine_config: RaggedInferenceEngineConfig) -> DSEmbeddingBase:
-    name = "ragged_embedding" if embed_config.sinusoid_base is None else "scaled_sinusoid_embedding"
+    widen = embed_config.widen_to_residual or embed_config.sinusoid_base is not None
+    name = "scaled_sinusoid_embedding" if widen else "ragged_embedding"
     return DSEmbeddingRegistry.instantiate_config(ConfigBundle(name=name, config=embed_config))
 
 
@@ -60,12 +64,17 @@ def instantiate_unembed(unembed_config: DSUnembedConfig, engine_config: RaggedIn
 
 def instantiate_recurrent_mixer(mixer_config: DSRecurrentMixerConfig,
                                 engine_config: RaggedInferenceEngineConfig) -> DSRecurrentMixerBase:
-    name = {"delta": "gated_delta_mixer", "ssd": "ssd_mixer"}.get(mixer_config.kind)
+    name = {"delta": "gated_delta_mixer", "ssd": "ssd_mixer", "mlstm": "mlstm_mixer"}.get(mixer_config.kind)
     if name is None:
-        raise ValueError(f"Unknown recurrent mixer kind {mixer_config.kind!r}; expected 'delta' or 'ssd'")
+        raise ValueError(f"Unknown recurrent mixer kind {mixer_config.kind!r}; expected 'delta', 'ssd' or 'mlstm'")
     return DSRecurrentMixerRegistry.instantiate_config(ConfigBundle(name=name, config=mixer_config))
 
 
 def instantiate_sandwich_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig) -> DSPreNormBase:
     """Pre- and post-norm around every sublayer on an fp32 residual stream."""
     return DSPreNormRegistry.instantiate_config(ConfigBundle(name="fp32_sandwich_rms", config=norm_config))
+
+
+def instantiate_scaled_post_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig) -> DSPostNormBase:
+    """Post-norm with one gain and a per-channel scale on an fp32 stream, optionally mixing the streams of all layers."""
+    return DSPostNormRegistry.instantiate_config(ConfigBundle(name="fp32_scaled_post_rms", config=norm_config))

@@ -11,7 +11,11 @@
  ``ragged_unembed``           (norm +) last-token gather + vocabulary GEMM
  ``sink_chunked_attention``   bias + unit-RMS q/k + cache append (``sxb_qk_norm_append``), causal or chunk-local softmax
                               with a sink logit over the paged cache in fp32 (``sxb_sink_attention``)
- ``scaled_sinusoid_embedding``  token row * scale + sinusoidal position vector into an fp32 residual
+ ``scaled_sinusoid_embedding``  token row * scale (+ sinusoidal position vector) into an fp32 residual
+ ``latent_sink_attention``    keys / values as up-projections of one cached latent per token (+ a shared rotated key
+                              part); attention in the latent space, sliding window, sink logit
+ ``mlstm_mixer``              matrix-memory LSTM: exponential gating with a running maximum around the linear recurrence
+ ``fp32_scaled_post_rms``     fp32 stream += scale (.) rms_norm(sublayer output) * gain (+ mixture of all layers' streams)
  ``fp32_sandwich_rms``        fp32 residual += post-norm(sublayer output); next pre-norm, one kernel
  ``gated_delta_mixer`` / ``ssd_mixer``   short convolutions with carried inputs + linear recurrence with a matrix
                               state per (sequence slot, head) + gated group norm
@@ -55,6 +59,8 @@ def _apply_activation(y: torch.Tensor, bias: Optional[torch.Tensor], act: Activa
         # fused weights are [gate | up] halves (HF gate_proj / up_proj order): act(gate) * up
         if bias is not None:
             y = y + bias
+        if y.is_cuda and (y.dtype != torch.bfloat16 or (y.shape[-1] // 2) % 8):
+            return M.gated_act_rows(y, _act_name(act))       # fp32 rows, or halves that are not 16-byte multiples
         return F.gated_act(y, _act_name(act))
     if act == ActivationType.IDENTITY:
         return y if bias is None else y + bias
@@ -224,7 +230,8 @@ class DSMultiGemmMoE(DSMoEBase):
 
     @staticmethod
     def supports_config(config: DSMoEConfig) -> bool:
-        return _dt(config.input_dtype) == _dt(config.output_dtype) and config.top_k in (1, 2, 4, 8)
+        return (_dt(config.input_dtype) == _dt(config.output_dtype) and 1 <= config.top_k <= 8
+                and config.top_k <= config.n_experts and config.score_function in ("softmax", "sigmoid"))
 
     def __init__(self, config, implementation_config):
         super().__init__(config, implementation_config)
@@ -241,16 +248,25 @@ class DSMultiGemmMoE(DSMoEBase):
 
     def forward(self, hidden_states, gate_w, mlp_1_w, mlp_2_w, mlp_1_b=None, mlp_2_b=None) -> torch.Tensor:
         c = self._config
-        logits = torch.nn.functional.linear(hidden_states, gate_w)
-        scores, assign, offsets, counts = moe_ops.top_k_gating(logits, c.top_k, renormalize=c.normalize_scores)
+        if c.router_dtype is not None and _dt(c.router_dtype).torch != hidden_states.dtype:
+            rd = _dt(c.router_dtype).torch
+            logits = torch.nn.functional.linear(hidden_states.to(rd), gate_w.to(rd))
+        else:
+            logits = torch.nn.functional.linear(hidden_states, gate_w)
+        scores, assign, offsets, counts = moe_ops.top_k_gating(logits, c.top_k, renormalize=c.normalize_scores,
+                                                               score_function=c.score_function)
         from .....moe import fused_ep
         if fused_ep.grouped_inference_ok(hidden_states, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b):
             # one grouped tcgen05 GEMM per projection over expert-contiguous rows, no host synchronisation
             self._output = fused_ep.grouped_experts_inference(
                 hidden_states, scores, assign, offsets, counts, mlp_1_w, mlp_2_w,
-                lambda t: _apply_activation(t, None, c.activation), c.top_k)
+                lambda t: _apply_activation(t, None, c.activation), c.top_k, weight_input=c.weight_input)
             return self._output
-        moe_in, cumsum, slots = moe_ops.moe_scatter(hidden_states, assign, offsets, counts)
+        if c.weight_input:
+            moe_in, cumsum, slots = moe_ops.moe_scatter_scaled(hidden_states, scores, assign, offsets, counts)
+            scores = None                   # the outputs are summed as they are
+        else:
+            moe_in, cumsum, slots = moe_ops.moe_scatter(hidden_states, assign, offsets, counts)
         out = torch.empty_like(moe_in)
         lo = 0
         for e, hi in enumerate(cumsum.tolist()):
@@ -405,7 +421,7 @@ class DSScaledSinusoidEmbedding(DSEmbeddingBase):
 
     @staticmethod
     def supports_config(config: DSEmbeddingsConfig) -> bool:
-        return (config.sinusoid_base is not None and not config.use_token_type and not config.positional_embedding
+        return (not config.use_token_type and not config.positional_embedding
                 and _dt(config.residual_dtype) == DtypeEnum.fp32)
 
     def __init__(self, config, implementation_config):
@@ -547,3 +563,166 @@ class DSStateSpaceDualMixer(_RecurrentMixer):
                                 info, H, G, n, dv, False)
         return M.group_norm_gate(y, projected[:, :inner], weights.norm, inner // c.norm_groups, c.eps, True,
                                  _dt(c.output_dtype).torch)
+
+
+@DSRecurrentMixerRegistry.register_module
+class DSMatrixLSTMMixer(_RecurrentMixer):
+    """Matrix-memory LSTM.  Projection columns: ``q (H n) | k (H n) | v (H dv) | gate (H dv) | i (H) | f (H)``.  Log gates
+    ``i = cap tanh((i + b_i) / cap)``, ``f = logsigmoid(cap tanh((f + b_f) / cap))``; with a running maximum ``m`` (0 at
+    the start) ``m_t = max(f + m, i)``, ``S <- exp(f + m - m_t) S + exp(i - m_t) k v^T``, ``z`` likewise with ``k`` alone,
+    ``o = S^T q / (max(|z . q|, exp(-m_t)) + 1e-6)`` with ``q`` scaled by ``n^-1/2``; the output is ``o / rms(o)`` per
+    head times ``norm`` times ``sigmoid(gate)``.  ``z`` is carried as one more value channel that is always 1, so the
+    state per head is ``[dv + 1, n]`` and the recurrence the same kernel the other mixers use."""
+
+    @staticmethod
+    def name() -> str:
+        return "mlstm_mixer"
+
+    @staticmethod
+    def supports_config(config: DSRecurrentMixerConfig) -> bool:
+        return (config.kind == "mlstm" and config.key_dim <= 256 and config.n_heads == config.n_heads_kv
+                and config.gate_cap > 0.0)
+
+    @property
+    def conv_channels(self) -> int:
+        return 0
+
+    @property
+    def projection_width(self) -> int:
+        c = self._config
+        return 2 * c.n_heads * (c.key_dim + c.value_dim) + 2 * c.n_heads
+
+    def state_shapes(self):
+        """Matrix state with the normaliser as its last row per head, and the running maximum."""
+        c = self._config
+        return [((c.n_heads, c.value_dim + 1, c.key_dim), torch.float32), ((c.n_heads,), torch.float32)]
+
+    def forward(self, projected, weights, states, batch):
+        c = self._config
+        H, n, dv = c.n_heads, c.key_dim, c.value_dim
+        S, m = states
+        info = batch.seq_info()
+        g0 = 2 * H * n + H * dv
+        i0 = g0 + H * dv
+        decay, beta, mt = M.mlstm_gate_scan(projected[:, i0: i0 + H], projected[:, i0 + H: i0 + 2 * H], weights.gate_bias_i,
+                                            weights.gate_bias_f, c.gate_cap, m, info)
+        x = M.mlstm_prepare(projected, H, n, dv, n ** -0.5)
+        o = M.linear_recurrence(x[:, H * n: 2 * H * n], x[:, : H * n], x[:, 2 * H * n:], decay, beta, None, S, info, H, H,
+                                n, dv + 1, False)
+        return M.mlstm_output(o, mt, projected[:, g0: g0 + H * dv], weights.norm, H, dv, c.eps,
+                              _dt(c.output_dtype).torch)
+
+
+@DSSelfAttentionRegistry.register_module
+class DSLatentSinkAttention(DSSelfAttentionBase):
+    """Attention whose keys and values are up-projections of one normalised latent vector per token.  The paged cache
+    holds, per token, that latent (``kv_latent_dim`` channels) followed by one rotated key part (``rope_head_dim``
+    channels, interleaved pairs) shared by all heads -- nothing per head.  Queries come through a normalised latent of
+    their own.  The up-projections never run over the cache: a query head's unrotated part is carried through the key
+    up-projection (``q_abs = W_uk[h]^T q``), attention runs in the latent space with ``[q_abs | q_rot]`` against
+    ``[latent | k_rot]`` and the latent itself as value, and the value up-projection is applied to the attended latent.
+    Causal or sliding-window mask, optional sink logit; scores, weights and the weighted sum are fp32.
+
+    ``forward(projected, cache, batch, inv_freqs, weights)``: ``projected`` ``[T, q_rank + kv_latent_dim +
+    rope_head_dim (+ padding)]`` is the fused down-projection; ``weights`` has ``q_norm``, ``w_uq`` ``[H (d + rot),
+    q_rank]``, ``kv_norm``, ``w_uk`` ``[H, d, r]``, ``w_uv_t`` ``[H, r, dv]`` and ``sink``.  Returns ``[T, H dv]``."""
+
+    @staticmethod
+    def name() -> str:
+        return "latent_sink_attention"
+
+    @staticmethod
+    def supports_config(config: DSSelfAttentionConfig) -> bool:
+        if config.kv_latent_dim is None or config.rope_head_dim < 0 or config.n_heads_kv != 1:
+            return False
+        if MaskingType(config.masking_type) not in (MaskingType.causal, MaskingType.sliding_window):
+            return False
+        if MaskingType(config.masking_type) == MaskingType.sliding_window and int(config.masking_args.get("size", 0)) < 1:
+            return False
+        return PositionalEmbeddingType(config.positional_embedding_type) in (PositionalEmbeddingType.none,
+                                                                             PositionalEmbeddingType.rotate_every_other)
+
+    def __init__(self, config: DSSelfAttentionConfig, implementation_config: Dict[str, Any]) -> None:
+        super().__init__(config, implementation_config)
+        rot = config.positional_embedding_config
+        n_rot = 0
+        if PositionalEmbeddingType(config.positional_embedding_type) == PositionalEmbeddingType.rotate_every_other:
+            n_rot = config.rope_head_dim if rot is None or rot.rotate_dim is None else rot.rotate_dim
+        if n_rot % 2 or n_rot > config.rope_head_dim:
+            raise ValueError(f"cannot rotate {n_rot} of {config.rope_head_dim} channels in pairs")
+        base = 10000.0 if rot is None else rot.theta_base
+        self._inv_freq = torch.pow(torch.tensor(float(base), dtype=torch.float32),
+                                   -torch.arange(0, n_rot, 2, dtype=torch.float32) / max(n_rot, 1))
+
+    @property
+    def kv_block_size(self) -> int:
+        return 64
+
+    @property
+    def q_block_size(self) -> int:
+        return 1
+
+    @property
+    def cache_row(self) -> int:
+        return self._config.kv_latent_dim + self._config.rope_head_dim
+
+    MAX_VALUE_COLS = 256        # the attention kernels hold at most this many value channels per query head
+
+    def forward(self, projected: torch.Tensor, kv_cache, batch, inv_freqs=None, weights=None) -> torch.Tensor:
+        c = self._config
+        H, d, rot, r, dv = c.n_heads_q, c.head_size, c.rope_head_dim, c.kv_latent_dim, c.v_head_size or c.head_size
+        cache = kv_cache[0] if isinstance(kv_cache, (tuple, list)) else kv_cache
+        T = projected.shape[0]
+        q_rank = weights.w_uq.shape[1]
+        if self._inv_freq.device != projected.device:
+            self._inv_freq = self._inv_freq.to(projected.device)
+        t2s, pos, tables = batch.token_to_seq(), batch.token_positions(), batch.block_tables()
+        cq = M.rms_norm_slice(projected[:, :q_rank], weights.q_norm, c.qk_norm_eps)
+        q = F.linear(cq, weights.w_uq)                                         # [T, H (d + rot)]
+        q_nope = q.view(T, H, d + rot)[:, :, :d].transpose(0, 1)              # [H, T, d]
+        q_abs = torch.bmm(q_nope, weights.w_uk).transpose(0, 1)               # [T, H, r], strided
+        qf = M.latent_qk_prepare(q, q_abs, projected[:, q_rank: q_rank + r + rot], weights.kv_norm, self._inv_freq, cache,
+                                 t2s, pos, tables, H, d, rot, c.qk_norm_eps)
+        window = int(c.masking_args["size"]) if MaskingType(c.masking_type) == MaskingType.sliding_window else 0
+        out_dt = _dt(c.output_dtype).torch
+        atoms, n_long = None, 0
+        if qf.is_cuda and hasattr(batch, "atoms_longer_than"):
+            atoms, n_long = batch.atoms(), batch.atoms_longer_than(M.SHORT_ATOM)
+        sink = weights.sink if c.sink else None
+        if r <= self.MAX_VALUE_COLS:
+            lat = M.sink_attention(qf, cache, None, sink, t2s, pos, tables, c.scale_factor, 0, out_dt, atoms, n_long,
+                                   window=window, value_cols=r)
+        else:
+            # wider latents: the value channels in parts, each a pass over the keys with the same weights
+            parts = []
+            for c0 in range(0, r, self.MAX_VALUE_COLS):
+                n = min(self.MAX_VALUE_COLS, r - c0)
+                parts.append(M.sink_attention(qf, cache, None, sink, t2s, pos, tables, c.scale_factor, 0, out_dt, None, 0,
+                                              window=window, value_cols=n, value_col0=c0).view(T, H, n))
+            lat = torch.cat(parts, dim=2)
+        ctx = torch.bmm(lat.view(T, H, r).transpose(0, 1), weights.w_uv_t)     # [H, T, dv]
+        return ctx.transpose(0, 1).reshape(T, H * dv)
+
+
+@DSPostNormRegistry.register_module
+class DSScaledPostRMSNorm(DSPostNormBase):
+    """Post-norm on the sublayer's output only, on an fp32 stream: ``x <- x + scale (.) (rms_norm(hidden) * gain)`` with
+    ONE gain for all channels and a per-channel ``scale``.  With ``mix`` the result is also stored as the next entry of
+    a stack of streams and the stream handed on is their weighted sum (``mix = (stack, n_prev, weights, out)``)."""
+
+    @staticmethod
+    def name() -> str:
+        return "fp32_scaled_post_rms"
+
+    @staticmethod
+    def supports_config(config: DSNormConfig) -> bool:
+        return NormTypeEnum(config.type) == NormTypeEnum.RMSNorm and _dt(config.residual_dtype) == DtypeEnum.fp32
+
+    def forward(self, residual, hidden_states, gamma, beta=None, scale=None, out=None, mix=None):
+        out = residual if out is None else out
+        if mix is None:
+            M.post_norm_mix(residual, hidden_states, gamma, scale, out, self._config.eps)
+        else:
+            stack, n_prev, w, mixed = mix
+            M.post_norm_mix(residual, hidden_states, gamma, scale, out, self._config.eps, stack, n_prev, w, mixed)
+        return out

@@ -18,18 +18,24 @@ from ..native import lib as _lib
 _lib.register({
     "sxb_top_k_gating": "ppppp" "iiii" "i" "p",
     "sxb_moe_scatter": "ppppppp" "iiiii" "p",
+    "sxb_moe_scatter_scaled": "pppppppp" "iiiii" "p",
     "sxb_moe_gather": "pppp" "iii" "p",
     "sxb_moe_gather_bwd": "pppppp" "iii" "p",
 })
 
 
-def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True):
+def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True, score_function: str = "softmax"):
     """``logits`` [T, E] -> ``(scores fp32 [T,K], assignments int32 [T,K], offsets int32 [T,K], counts int32 [E])``.
+
+    ``score_function`` ``"softmax"``: scores are the softmax over all experts; ``"sigmoid"``: every expert is scored on
+    its own with ``sigmoid(logit)``.  The ``top_k`` largest win either way; ``renormalize`` divides them by their sum.
 
     ``offsets[t,k]`` is the arrival index of token ``t`` inside expert ``assignments[t,k]`` (a permutation of
     ``range(counts[e])`` per expert; on CUDA the order is nondeterministic, on CPU it is token order)."""
     T, E = logits.shape
     dev = logits.device
+    if score_function not in ("softmax", "sigmoid"):
+        raise ValueError(f"unknown score function {score_function!r}")
     scores = torch.empty(T, top_k, dtype=torch.float32, device=dev)
     assign = torch.empty(T, top_k, dtype=torch.int32, device=dev)
     offsets = torch.empty(T, top_k, dtype=torch.int32, device=dev)
@@ -37,9 +43,10 @@ def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True):
     if logits.is_cuda:
         logits = logits.contiguous()
         _lib.call("sxb_top_k_gating", logits.data_ptr(), scores.data_ptr(), assign.data_ptr(), offsets.data_ptr(),
-                  counts.data_ptr(), T, E, top_k, int(renormalize), _lib.dtype_code(logits.dtype), _lib.stream_ptr())
+                  counts.data_ptr(), T, E, top_k, int(bool(renormalize)) | (2 if score_function == "sigmoid" else 0),
+                  _lib.dtype_code(logits.dtype), _lib.stream_ptr())
         return scores, assign, offsets, counts
-    probs = torch.softmax(logits.float(), dim=-1)
+    probs = torch.sigmoid(logits.float()) if score_function == "sigmoid" else torch.softmax(logits.float(), dim=-1)
     s, a = torch.topk(probs, top_k, dim=-1)
     if renormalize:
         s = s / s.sum(dim=-1, keepdim=True)
@@ -134,3 +141,26 @@ def moe_scatter(x: torch.Tensor, assign: torch.Tensor, offsets: torch.Tensor, co
 def moe_gather(moe_output: torch.Tensor, scores: torch.Tensor, mapped_slots: torch.Tensor) -> torch.Tensor:
     """``out[t] = sum_k scores[t,k] * moe_output[mapped_slots[t,k]]`` (differentiable in both tensor arguments)."""
     return _MoEGather.apply(moe_output, scores, mapped_slots)
+
+
+@torch.no_grad()
+def moe_scatter_scaled(x: torch.Tensor, scores: torch.Tensor, assign: torch.Tensor, offsets: torch.Tensor,
+                       counts: torch.Tensor):
+    """:func:`moe_scatter` for layers whose routing weight multiplies the expert's INPUT: row ``(t, k)`` of the grouped
+    input is ``x[t] * scores[t, k]`` (product in fp32, rounded once to ``x.dtype``).  Inference only; bf16 or fp32 rows
+    of any width."""
+    T, H = x.shape
+    K, E = assign.shape[1], counts.shape[0]
+    if x.is_cuda:
+        x = x.contiguous()
+        moe_in = torch.empty(T * K, H, dtype=x.dtype, device=x.device)
+        cumsum = torch.empty(E, dtype=torch.int64, device=x.device)
+        slots = torch.empty(T, K, dtype=torch.int32, device=x.device)
+        _lib.call("sxb_moe_scatter_scaled", x.data_ptr(), scores.data_ptr(), moe_in.data_ptr(), assign.data_ptr(),
+                  offsets.data_ptr(), counts.data_ptr(), cumsum.data_ptr(), slots.data_ptr(), T, E, K, H,
+                  _lib.dtype_code(x.dtype), _lib.stream_ptr())
+        return moe_in, cumsum, slots
+    moe_in, cumsum, slots = _scatter_fwd(x, assign, offsets, counts)
+    scaled = (x.float()[:, None, :] * scores[:, :, None]).to(x.dtype).reshape(T * K, H)
+    moe_in[slots.long().reshape(-1)] = scaled
+    return moe_in, cumsum, slots
