@@ -181,6 +181,7 @@ __device__ __forceinline__ void push_body(const PushArgs& A) {
     }
     const int t = (int)(w / A.K);
     const int e = A.assign[w];
+    if ((unsigned)e >= (unsigned)A.E) continue;      // an assignment outside the expert table addresses no buffer
     const int row = A.tables[e] + A.offsets[w];
     const int d = e / A.L;
     const float wt = A.weights ? A.weights[w] : 1.f;

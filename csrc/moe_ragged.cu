@@ -71,6 +71,8 @@ top_k_gating_kernel(const T* __restrict__ logits, float* __restrict__ scores, in
       const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
     }
+    // logits that compare with nothing (NaN) leave no winner: fall back to expert k so that every index stays valid
+    if (best_e >= n_experts) best_e = k;
     // remove the winner from its owner lane
 #pragma unroll
     for (int i = 0; i < PER; ++i)

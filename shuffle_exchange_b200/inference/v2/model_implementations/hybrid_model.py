@@ -130,6 +130,7 @@ class DSHybridModel(DSInferenceModelBase):
         self._cache_of_run: Dict[int, int] = {}
         self._state_of_run: Dict[int, Tuple[int, ...]] = {}
         self._conv_of_run: Dict[int, Tuple[int, int]] = {}
+        self.layer_outputs = None        # set to a list: the stream every layer run hands on is appended (a copy)
         self._build_modules()
 
     # ------------------------------------------------------------------------------------------ construction
@@ -320,6 +321,8 @@ class DSHybridModel(DSInferenceModelBase):
             if not last:
                 y = self._feed_forward(L, lw, self._filtered(x, lw.conv2, c2, batch), li)
                 x = close(x, y, lw.norm2, lw.ls2, True)
+            if self.layer_outputs is not None:
+                self.layer_outputs.append(x.clone())
         rows = batch.last_token_index()
         if rows.numel() == 0:               # a step that only advances caches and states
             return torch.empty(0, s.vocab_size, dtype=torch.float32, device=x.device)
