@@ -193,10 +193,15 @@ def _attend_latent(q, rows, sink, scale, window, block_size, dv, pos0=0, tiled=T
     atoms, n_long = None, 0
     if tiled and 16 < Tq <= 128 and d % 4 == 0 and dv % 4 == 0:      # a prompt portion: the tiled kernel where there is one
         atoms, n_long = torch.tensor([[0, 0, Tq, pos0, 0, pos0 + Tq]], dtype=torch.int32, device=DEV), 1
-    out = M.sink_attention(q.to(DEV).contiguous(), cache.to(DEV), None, None if sink is None else sink.to(DEV),
-                           torch.zeros(Tq, dtype=torch.int32, device=DEV), pos.to(DEV), tables.to(DEV), scale, 0,
-                           torch.float32, atoms, n_long, window=window, value_cols=dv)
-    return out.cpu().view(Tq, Hq, dv)
+    parts = []
+    for c0 in range(0, dv, 256):                  # one pass holds at most 256 value channels
+        n = min(256, dv - c0)
+        out = M.sink_attention(q.to(DEV).contiguous(), cache.to(DEV), None, None if sink is None else sink.to(DEV),
+                               torch.zeros(Tq, dtype=torch.int32, device=DEV), pos.to(DEV), tables.to(DEV), scale, 0,
+                               torch.float32, atoms if dv <= 256 else None, n_long if dv <= 256 else 0, window=window,
+                               value_cols=n, value_col0=c0)
+        parts.append(out.cpu().view(Tq, Hq, n))
+    return torch.cat(parts, dim=2)
 
 
 @pytest.mark.parametrize("window,block_size,T", [(6, 4, 40), (8, 8, 40), (17, 16, 40), (1, 4, 12), (257, 16, 300), (0, 4, 40)])
