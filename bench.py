@@ -57,6 +57,9 @@ def parse():
                     help="instead of the training step: serving throughput (prefill and decode through the ragged "
                          "engine) of the hybrid Fomalix stack beside a Llama stack of equal size, for the comma-separated "
                          "sizes (w1024, w2048, w4096; 'all'), with device times of their kernels against the memory roofline")
+    ap.add_argument("--serve-model", default="fomalix", choices=["fomalix", "kekopel"],
+                    help="with --serve: 'kekopel' measures the Kekopel stack beside the Fomalix stack of equal size (and "
+                         "each of its kernels beside the like Fomalix kernel) instead of Fomalix beside Llama")
     ap.add_argument("--serve-prefill", type=int, default=4096)
     ap.add_argument("--serve-batch", type=int, default=64)
     ap.add_argument("--serve-context", type=int, default=2560)
@@ -475,7 +478,7 @@ def main():
         from shuffle_exchange_b200.inference.v2 import serve_bench
         sizes = list(serve_bench.SIZES) if args.serve == "all" else args.serve.split(",")
         print(json.dumps(serve_bench.run(sizes, args.serve_prefill, args.serve_batch, args.serve_context, args.steps,
-                                         args.warmup, chunk=args.serve_chunk)))
+                                         args.warmup, chunk=args.serve_chunk, model=args.serve_model)))
         return
     if args.impl == "reference":
         try:

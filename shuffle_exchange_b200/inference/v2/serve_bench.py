@@ -1,6 +1,9 @@
 """Serving throughput of a hybrid (Fomalix) stack next to a Llama stack of equal width, depth and feed-forward size, both
 through ``InferenceEngineV2.put`` with random weights, plus device times of the hybrid stack's kernels and of their Llama
-counterparts against the memory roofline.  ``bench.py --serve`` prints the result as one JSON object.
+counterparts against the memory roofline.  ``bench.py --serve`` prints the result as one JSON object.  With
+``--serve-model kekopel`` the pair is a Kekopel stack (latent attention with a sliding window, matrix-memory LSTM,
+post-scaled layers, dense and expert feed-forwards) next to the Fomalix stack of equal size, and the kernel table sets
+every Kekopel kernel beside the Fomalix kernel that does the like job.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up forwards, a buffer larger than L2 is rewritten between timed
 forwards.  Prefill: one request of ``prefill`` tokens in one forward.  Decode: ``batch`` requests with ``context`` tokens
@@ -253,11 +256,255 @@ def kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs
     return rows
 
 
+# ------------------------------------------------------------------------------------------------ Kekopel beside Fomalix
+WINDOW = 1024         # sliding window of the latent attention layers
+LATENT = dict(q_rank=512, kv_rank=192, rot=64)      # the cached row is kv_rank + rot = 256 channels
+
+
+def kekopel_config(z: Dict) -> Dict:
+    kinds = ["latent_attention", "mlstm", "latent_attention"]
+    mixers = {
+        "latent_attention": {"dim": z["head"], "heads": z["heads"], "kv_rank": LATENT["kv_rank"],
+                             "mask": {"size": WINDOW}, "q_rank": LATENT["q_rank"],
+                             "rot": {"base": 10000.0, "dims": LATENT["rot"]}, "rot_dim": LATENT["rot"],
+                             "scale": (z["head"] + LATENT["rot"]) ** -0.5, "vdim": z["head"]},
+        "mlstm": {"dim": z["head"], "gate_cap": 15.0, "heads": z["heads"], "vdim": z["head"]},
+    }
+    mlps = [{"ff": z["ff"], "kind": "dense"},
+            {"expert": {"ff": z["ff"] // 4}, "kind": "moe", "router": {"experts": 8, "top": 2}}]
+    layers = [{"type": kinds[i % 3], "mixer": mixers[kinds[i % 3]], "mlp": mlps[i % 2]} for i in range(z["layers"])]
+    return {"architecture": "Kekopel", "canon": {"taps": 4}, "layers": layers, "norm": {"eps": 1e-5}, "vocab": VOCAB,
+            "width": z["width"]}
+
+
+def kekopel_weights(cfg: Dict, device) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(0)
+    W = cfg["width"]
+    bf = torch.bfloat16
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g, device=device) / math.sqrt(i)).to(bf)
+
+    def vec(n, lo=0.5, hi=1.5):
+        return (torch.rand(n, generator=g, device=device) * (hi - lo) + lo).to(bf)
+
+    out = {"embed": mat(cfg["vocab"], W), "head": mat(cfg["vocab"], W), "final.norm": vec(1).reshape(())}
+    for i, L in enumerate(cfg["layers"]):
+        m, p = L["mixer"], f"l{i}."
+        for n in ("1", "2"):
+            out[p + "norm" + n], out[p + "ls" + n] = vec(1).reshape(()), vec(W, 0.2, 0.8)
+            out[p + "canon" + n] = vec(W * 4, -0.3, 0.3).view(W, 4)
+        out[p + "dwa"] = torch.cat([vec(i + 1, -0.1, 0.1), vec(1, 0.8, 1.0)])
+        if L["type"] == "latent_attention":
+            H, d, rot, dv, r, qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            out[p + "mix.dq"], out[p + "mix.dq.norm"], out[p + "mix.uq"] = mat(qr, W), vec(qr), mat(H * (d + rot), qr)
+            out[p + "mix.dkv"], out[p + "mix.dkv.norm"] = mat(r + rot, W), vec(r)
+            out[p + "mix.uk"], out[p + "mix.uv"] = mat(H * d, r), mat(H * dv, r)
+            out[p + "mix.sink"], out[p + "mix.o"] = vec(H, -1, 1), mat(W, H * dv)
+        else:
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            for n, o in (("q", H * d), ("k", H * d), ("v", H * dv), ("g", H * dv), ("i", H), ("f", H)):
+                out[p + "mix." + n] = mat(o, W)
+            out[p + "mix.i.b"], out[p + "mix.f.b"] = vec(H, -3, -1), vec(H, 2, 4)
+            out[p + "mix.norm"], out[p + "mix.o"] = vec(H * dv), mat(W, H * dv)
+        mlp = L["mlp"]
+        if mlp["kind"] == "dense":
+            out[p + "mlp.up"], out[p + "mlp.up.b"] = mat(mlp["ff"], W), vec(mlp["ff"], -0.1, 0.1)
+            out[p + "mlp.down"], out[p + "mlp.down.b"] = mat(W, mlp["ff"]), vec(W, -0.1, 0.1)
+        else:
+            F_ = mlp["expert"]["ff"]
+            out[p + "mlp.router"] = mat(mlp["router"]["experts"], W)
+            for e in range(mlp["router"]["experts"]):
+                out[p + f"mlp.e{e}.gate"], out[p + f"mlp.e{e}.up"] = mat(F_, W), mat(F_, W)
+                out[p + f"mlp.e{e}.down"] = mat(W, F_)
+    return out
+
+
+def build_kekopel(z: Dict, max_tokens: int, max_seqs: int, pages: int):
+    cfg = kekopel_config(z)
+    return build_engine_from_state_dict(cfg, kekopel_weights(cfg, "cuda"), _engine_config(max_tokens, max_seqs, pages),
+                                        dtype=torch.bfloat16)
+
+
+def kekopel_kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs: float,
+                         peak_tflops: Dict[str, float]) -> List[Dict]:
+    """Every Kekopel kernel beside the Fomalix kernel that does the like job (``like``), at prefill (one request) and
+    decode (``batch`` requests) shapes: device time, algorithmic bytes and FLOPs, fraction of the roofline (the larger
+    of bytes / copy bandwidth and FLOPs / the peak of the unit the products run on)."""
+    from ...moe import fused_ep
+    from ...ops import functional as F
+    from ...ops import moe_ops
+    from .kernels import mixer_ops as M
+    from .ragged.ragged_wrapper import RaggedBatchWrapper
+    dev, bf = "cuda", torch.bfloat16
+    W, H, G, d, ff = z["width"], z["heads"], z["kv_heads"], z["head"], z["ff"]
+    r, rot, qr = LATENT["kv_rank"], LATENT["rot"], LATENT["q_rank"]
+    rows: List[Dict] = []
+
+    def add(name, like, phase, fn, nbytes, flops=0.0, pipe=None):
+        ms = timer(fn, 5, 3)
+        ideal_ms = nbytes / hbm_gbs / 1e6
+        if pipe is not None:
+            ideal_ms = max(ideal_ms, flops / peak_tflops[pipe] / 1e9)
+        rows.append({"kernel": name, "like": like, "phase": phase, "ms": round(ms, 4),
+                     "GB_s": round(nbytes / ms / 1e6, 1), "GFLOP_s": round(flops / ms / 1e6, 1), "pipe": pipe or "memory",
+                     "of_roofline": round(ideal_ms / ms, 3)})
+
+    for phase, T, n_seq, seen in (("prefill", prefill, 1, 0), ("decode", batch, batch, context)):
+        per = T // n_seq
+        tot = seen + per
+        n_pages_seq = (tot + 63) // 64
+        t2s = torch.arange(n_seq, device=dev, dtype=torch.int32).repeat_interleave(per)
+        pos = (torch.arange(per, device=dev, dtype=torch.int32) + seen).repeat(n_seq)
+        tables = torch.arange(n_seq * n_pages_seq, device=dev, dtype=torch.int32).view(n_seq, n_pages_seq)
+        info = torch.tensor([[i * per, per, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        x32 = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        wv = torch.ones(W, device=dev, dtype=bf)
+        # stream: filter in front of a sublayer, post-norm (+ mixture of 4 streams) behind it
+        cw = torch.randn(W, 4, device=dev).to(bf)
+        cst = torch.zeros(n_seq, 3, W, device=dev)
+        add("conv_residual + state update", None, phase,
+            lambda: (M.conv_residual(x32, cw, cst, info, t2s, bf), M.conv_state_update(x32, cst, info)),
+            T * W * (4 + 2) + n_seq * 3 * W * 4 * 2)
+        xb = x32.to(bf)
+        cstb = torch.zeros(n_seq, 3, W, device=dev, dtype=bf)
+        add("conv_silu + state update", "conv_residual + state update", phase,
+            lambda: (M.conv_silu(xb, cw, None, cstb, info, t2s), M.conv_state_update(xb, cstb, info)),
+            T * W * (2 + 4) + n_seq * 3 * W * 2 * 2)
+        gain, ls = torch.ones(1, device=dev), torch.ones(W, device=dev)
+        stack = torch.randn(5, T, W, device=dev)
+        mixw, mixed = torch.ones(5, device=dev), torch.empty(T, W, device=dev)
+        add("post_norm_mix (no mixture)", None, phase,
+            lambda: M.post_norm_mix(x32, y, gain, ls, stack[4], 1e-5), T * W * (4 + 2 + 4))
+        add("post_norm_mix (mixture of 5 streams)", None, phase,
+            lambda: M.post_norm_mix(x32, y, gain, ls, stack[4], 1e-5, stack, 4, mixw, mixed), T * W * (4 + 2 + 4 + 4 * 4 + 4))
+        add("resid_norm_step", "post_norm_mix (no mixture)", phase,
+            lambda: M.resid_norm_step(x32, y, wv, None, wv, 1e-5, bf), T * W * (4 + 4 + 2 + 2))
+        # latent attention: prepare + attend
+        proj = torch.randn(T, qr + r + rot, device=dev).to(bf)
+        qn = torch.ones(qr, device=dev, dtype=bf)
+        add("rms_norm_slice (query latent)", None, phase, lambda: M.rms_norm_slice(proj[:, :qr], qn, 1e-5), T * qr * 4)
+        q = torch.randn(T, H * (d + rot), device=dev).to(bf)
+        q_abs = torch.randn(H, T, r, device=dev).to(bf).transpose(0, 1)
+        kn = torch.ones(r, device=dev, dtype=bf)
+        inv = torch.pow(torch.tensor(10000.0), -torch.arange(0, rot, 2, dtype=torch.float32) / rot).to(dev)
+        cache = torch.randn(n_seq * n_pages_seq, 64, 1, r + rot, device=dev).to(bf)
+        add("latent_qk_prepare", None, phase,
+            lambda: M.latent_qk_prepare(q, q_abs, proj[:, qr:], kn, inv, cache, t2s, pos, tables, H, d, rot, 1e-5),
+            T * ((r + rot) * 4 + H * (r + rot) * (2 + 4)))
+        qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+        bias = torch.zeros((H + 2 * G) * d, device=dev, dtype=bf)
+        kc = torch.randn(n_seq * n_pages_seq, 64, G, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * n_pages_seq, 64, G, d, device=dev).to(bf)
+        add("qk_norm_append", "latent_qk_prepare", phase,
+            lambda: M.qk_norm_append(qkv, bias, kc, vc, t2s, pos, tables, H, G, d, d, 1e-5, True),
+            T * ((H + 2 * G) * d * 2 + H * d * 4 + 2 * G * d * 2))
+        wrap = RaggedBatchWrapper(max(T, 64), n_seq, n_pages_seq, device=dev)
+
+        class _Seq:
+            def __init__(self, i):
+                self.seen_tokens, self._b = seen, tables[i].cpu()
+
+            def kv_blocks(self):
+                return self._b
+        for i in range(n_seq):
+            wrap.insert_sequence(_Seq(i), torch.zeros(per, dtype=torch.int32), do_checks=False)
+        wrap.finalize()
+        atoms, n_long = wrap.atoms(), wrap.atoms_longer_than(M.SHORT_ATOM)
+        sink = torch.zeros(H, device=dev)
+        ql = torch.randn(T, H, r + rot, device=dev)
+        if phase == "prefill":
+            keys_per_q = sum(min(p + 1, WINDOW) for p in range(per)) / per
+            keys_read = n_seq * tot
+        else:
+            keys_per_q = min(tot, WINDOW)
+            keys_read = n_seq * min(tot, WINDOW)
+        add(f"sink_attention, latent rows (window {WINDOW})", None, phase,
+            lambda: M.sink_attention(ql, cache, None, sink, t2s, pos, tables, 0.06, 0, bf, atoms, n_long, window=WINDOW,
+                                     value_cols=r),
+            keys_read * (r + rot) * 2 + T * H * ((r + rot) * 4 + r * 2), 2.0 * T * H * (2 * r + rot) * keys_per_q, "fp32")
+        q32 = torch.randn(T, H, d, device=dev)
+        add(f"sink_attention, per-head keys (chunk {WINDOW})", f"sink_attention, latent rows (window {WINDOW})", phase,
+            lambda: M.sink_attention(q32, kc, vc, sink, t2s, pos, tables, d ** -0.5, WINDOW, bf, atoms, n_long),
+            n_seq * (tot if phase == "prefill" else (tot - (tot - 1) // WINDOW * WINDOW)) * 2 * G * d * 2 + T * H * d * 6,
+            4.0 * T * H * d * ((min(per, WINDOW) + 1) / 2 if phase == "prefill" else (tot - (tot - 1) // WINDOW * WINDOW)),
+            "fp32")
+        # matrix-memory LSTM beside the state-space recurrence of the same head count and sizes
+        Pw = 2 * H * d + 2 * H * d + 2 * H
+        pm = torch.randn(T, (Pw + 7) // 8 * 8, device=dev).to(bf)
+        bi, bfg = torch.zeros(H, device=dev), torch.ones(H, device=dev)
+        mst = torch.zeros(n_seq, H, device=dev)
+        i0 = 4 * H * d
+        add("mlstm_gate_scan", None, phase,
+            lambda: M.mlstm_gate_scan(pm[:, i0: i0 + H], pm[:, i0 + H: i0 + 2 * H], bi, bfg, 15.0, mst, info),
+            T * H * (2 * 2 + 3 * 4))
+        A_log, dtb = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        add("recurrence_gates", "mlstm_gate_scan", phase,
+            lambda: M.recurrence_gates(pm[:, i0: i0 + H], pm[:, i0 + H: i0 + 2 * H], A_log, dtb, "delta"),
+            T * H * (2 * 2 + 2 * 4))
+        add("mlstm_prepare", None, phase, lambda: M.mlstm_prepare(pm, H, d, d, d ** -0.5),
+            T * (3 * H * d * 2 + (3 * H * d + H) * 4))
+        xm = M.mlstm_prepare(pm, H, d, d, d ** -0.5)
+        xm[:, : 2 * H * d] /= math.sqrt(d)
+        decay, beta = torch.rand(T, H, device=dev) * 0.1 + 0.9, torch.rand(T, H, device=dev)
+        S1 = torch.zeros(n_seq, H, d + 1, d, device=dev)
+        sb = (2 if seen else 1) * 4
+        add("linear_recurrence (mlstm, values + normaliser)", None, phase,
+            lambda: M.linear_recurrence(xm[:, H * d: 2 * H * d], xm[:, : H * d], xm[:, 2 * H * d:], decay, beta, None, S1,
+                                        info, H, H, d, d + 1, False),
+            n_seq * H * (d + 1) * d * sb + T * ((3 * H * d + H) * 4 + H * (d + 1) * 4), 4.0 * T * H * (d + 1) * d, "fp32")
+        xs = torch.randn(T, 3 * H * d, device=dev)
+        xs[:, : 2 * H * d] /= math.sqrt(d)
+        S0 = torch.zeros(n_seq, H, d, d, device=dev)
+        add("linear_recurrence (same sizes, no normaliser)", "linear_recurrence (mlstm, values + normaliser)", phase,
+            lambda: M.linear_recurrence(xs[:, H * d: 2 * H * d], xs[:, : H * d], xs[:, 2 * H * d:], decay, beta, None, S0,
+                                        info, H, H, d, d, False),
+            n_seq * H * d * d * sb + T * (3 * H * d * 4 + H * d * 4), 4.0 * T * H * d * d, "fp32")
+        o1 = torch.randn(T, H * (d + 1), device=dev)
+        mt = torch.zeros(T, H, device=dev)
+        gate = torch.randn(T, H * d, device=dev).to(bf)
+        nw = torch.ones(H * d, device=dev, dtype=bf)
+        add("mlstm_output", None, phase, lambda: M.mlstm_output(o1, mt, gate, nw, H, d, 1e-5, bf),
+            T * H * ((d + 1) * 4 + d * (2 + 2)))
+        o0 = torch.randn(T, H * d, device=dev)
+        add("group_norm_gate", "mlstm_output", phase, lambda: M.group_norm_gate(o0, gate, nw[:d], d, 1e-5, False, bf),
+            T * H * d * (4 + 2 + 2))
+        # feed-forwards
+        hu = torch.randn(T, ff, device=dev).to(bf)
+        bu = torch.zeros(ff, device=dev, dtype=bf)
+        add("bias_act_rows (squared relu)", None, phase, lambda: M.bias_act_rows(hu, bu, "relu_sq"), T * ff * 4)
+        hg = torch.randn(T, 2 * ff, device=dev).to(bf)
+        add("gated_act", "bias_act_rows (squared relu)", phase, lambda: F.gated_act(hg, "gelu"), T * ff * 6)
+        E, K, Fe = 8, 2, ff // 4
+        logits = torch.randn(T, E, device=dev)
+        xe = torch.randn(T, W, device=dev).to(bf)
+        w1 = (torch.randn(E, 2 * Fe, W, device=dev) / math.sqrt(W)).to(bf)
+        w2 = (torch.randn(E, W, Fe, device=dev) / math.sqrt(Fe)).to(bf)
+        moe_bytes = E * 3 * Fe * W * 2 + T * W * 2 * (1 + 2 * K + 1) + T * K * 3 * Fe * 2
+        moe_flops = 2.0 * T * K * 3 * Fe * W
+
+        def experts(score_function, weight_input):
+            s, a, o, c = moe_ops.top_k_gating(logits, K, renormalize=False, score_function=score_function)
+            return fused_ep.grouped_experts_inference(xe, s, a, o, c, w1, w2, F.swiglu, K, weight_input=weight_input)
+        add("experts: sigmoid gating, weighted rows in, grouped GEMMs, plain sum", None, phase,
+            lambda: experts("sigmoid", True), moe_bytes, moe_flops, "bf16")
+        add("experts: softmax gating, rows in, grouped GEMMs, weighted sum", "experts: sigmoid gating, weighted rows in, "
+            "grouped GEMMs, plain sum", phase, lambda: experts("softmax", False), moe_bytes, moe_flops, "bf16")
+    by_name = {(r_["kernel"], r_["phase"]): r_ for r_ in rows}
+    for r_ in rows:                      # distance from the roofline relative to the like kernel's
+        if r_["like"]:
+            mine = by_name[(r_["like"], r_["phase"])]
+            mine["like_of_roofline"] = r_["of_roofline"]
+            mine["like_kernel"] = r_["kernel"]
+    return rows
+
+
 def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, warmup: int, kernels: bool = True,
-        chunk: int = 0) -> Dict:
-    global CHUNK
+        chunk: int = 0, model: str = "fomalix") -> Dict:
+    global CHUNK, WINDOW
     if chunk > 0:
-        CHUNK = chunk
+        CHUNK = WINDOW = chunk
     peaks = {}
     p = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "MEASURED_PEAKS.json")
     if os.path.isfile(p):
@@ -274,6 +521,20 @@ def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, wa
            "attention_chunk": CHUNK, "fp32_fma_tflops_nominal": round(peak_tflops["fp32"], 1),
            "bf16_tflops_denominator": peak_tflops["bf16"],
            "sizes": {}}
+    if model == "kekopel":
+        out["metric"] = "serving tokens/s, Kekopel vs hybrid (Fomalix) stack of equal size"
+        out["attention_window"], out["latent"] = WINDOW, LATENT
+        CHUNK = WINDOW                   # the Fomalix stack's chunks are as long as the Kekopel stack's window
+        out["attention_chunk"] = CHUNK
+        for name in sizes:
+            z = SIZES[name]
+            entry = {"config": z,
+                     "kekopel": engine_throughput(build_kekopel, z, prefill, batch, context, steps, warmup, timer),
+                     "fomalix": engine_throughput(build_hybrid, z, prefill, batch, context, steps, warmup, timer)}
+            if kernels:
+                entry["kernels"] = kekopel_kernel_table(z, prefill, batch, context, timer, hbm, peak_tflops)
+            out["sizes"][name] = entry
+        return out
     for name in sizes:
         z = SIZES[name]
         entry = {"config": z,
