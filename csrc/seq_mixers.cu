@@ -553,13 +553,15 @@ static int attention_rows(int dtype, dim3 grid, const void* q, const void* kcach
                           int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
   const int group = Hq / G;
   int rc = SXB_OK;
+  // (Taking fewer heads together when a decode batch leaves SMs idle was measured slower: every CTA walks all keys.)
+  const int rep = group % 8 == 0 ? 8 : (group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1));
 #define ROWS(REP)                                                                                                      \
   SEQMIX_DISPATCH(dtype, (rc = launch_attention_rows<T, REP>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos,      \
                                                               tables, max_blocks, block_size, Hq, G, d, dv, scale,      \
                                                               chunk, window, kpitch, vpitch, atoms, s)))
-  if (group % 8 == 0) ROWS(8);
-  else if (group % 4 == 0) ROWS(4);
-  else if (group % 2 == 0) ROWS(2);
+  if (rep == 8) ROWS(8);
+  else if (rep == 4) ROWS(4);
+  else if (rep == 2) ROWS(2);
   else ROWS(1);
 #undef ROWS
   return rc;
@@ -1054,27 +1056,42 @@ rms_norm_slice_kernel(const T* __restrict__ x, long long ld, const T* __restrict
 }
 
 // out = act(in + bias) for rows of any width; act as in gated_act_rows plus 4 = relu(z)^2.
+__device__ __forceinline__ float act_f(float z, int act) {
+  if (act == 4) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (act == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (act == 3) return silu_f(z);
+  if (act == 1) return fmaxf(z, 0.f);
+  return z;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 bias_act_rows_kernel(const T* __restrict__ in, const T* __restrict__ bias, T* __restrict__ out, long long total, int F,
                      int act) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const float z = to_f32<T>(in[i]) + (bias ? to_f32<T>(bias[i % F]) : 0.f);
-  float a;
-  if (act == 4) {
-    const float r = fmaxf(z, 0.f);
-    a = r * r;
-  } else if (act == 2) {
-    a = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-  } else if (act == 3) {
-    a = silu_f(z);
-  } else if (act == 1) {
-    a = fmaxf(z, 0.f);
-  } else {
-    a = z;
-  }
-  out[i] = from_f32<T>(a);
+  out[i] = from_f32<T>(act_f(to_f32<T>(in[i]) + (bias ? to_f32<T>(bias[i % F]) : 0.f), act));
+}
+
+// 16 bytes per thread and access: widths that are multiples of 16 / sizeof(T), 16-byte aligned pointers.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_act_rows_vec_kernel(const T* __restrict__ in, const T* __restrict__ bias, T* __restrict__ out, long long total_vec,
+                         int F, int act) {
+  constexpr int E = 16 / (int)sizeof(T);
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_vec) return;
+  uint4 u = reinterpret_cast<const uint4*>(in)[i];
+  T* v = reinterpret_cast<T*>(&u);
+  uint4 ub = make_uint4(0u, 0u, 0u, 0u);
+  if (bias) ub = *reinterpret_cast<const uint4*>(bias + (i * E) % F);
+  const T* b = reinterpret_cast<const T*>(&ub);
+#pragma unroll
+  for (int e = 0; e < E; ++e) v[e] = from_f32<T>(act_f(to_f32<T>(v[e]) + (bias ? to_f32<T>(b[e]) : 0.f), act));
+  reinterpret_cast<uint4*>(out)[i] = u;
 }
 
 // ------------------------------------------------------------------------------------------------ latent attention
@@ -1163,30 +1180,34 @@ mlstm_prepare_kernel(const T* __restrict__ proj, long long ld, float* __restrict
   }
 }
 
-// One warp per (sequence, head): gates of 32 tokens at a time, the running maximum through a warp scan of the maps
-// m -> max(m + f, i).  i = cap tanh((raw_i + b_i) / cap), f = logsigmoid(cap tanh((raw_f + b_f) / cap)).
+// One CTA per (sequence, head): gates of blockDim.x tokens at a time, the running maximum through a scan of the maps
+// m -> max(m + f, i) (within the warps by shuffles, across them through shared memory).
+// i = cap tanh((raw_i + b_i) / cap), f = logsigmoid(cap tanh((raw_f + b_f) / cap)).
+constexpr int kScanThreads = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kScanThreads)
 mlstm_gate_scan_kernel(const T* __restrict__ raw_i, const T* __restrict__ raw_f, long long ld,
                        const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
                        float* __restrict__ mstate, float* __restrict__ decay, float* __restrict__ beta,
                        float* __restrict__ mt, const int* __restrict__ seq_info, int H) {
+  __shared__ float wa[kScanThreads / 32], wb[kScanThreads / 32], carry;
   const int* si = seq_info + 4 * blockIdx.x;
   const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
-  const int h = blockIdx.y, lane = threadIdx.x;
+  const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   float m = seen > 0 ? mstate[(long long)slot * H + h] : 0.f;
   const float bi = bias_i[h], bf = bias_f[h];
-  for (int t0 = 0; t0 < rows; t0 += 32) {
-    const int t = t0 + lane;
+  for (int t0 = 0; t0 < rows; t0 += blockDim.x) {
+    const int t = t0 + threadIdx.x;
     const bool valid = t < rows;
-    float ig = -INFINITY, fg = 0.f;
+    float ig = -INFINITY, fg = 0.f;                 // rows past the end hold the identity map
     if (valid) {
       const long long o = (long long)(first + t) * ld + h;
       ig = cap * tanhf((to_f32<T>(raw_i[o]) + bi) / cap);
       const float fr = cap * tanhf((to_f32<T>(raw_f[o]) + bf) / cap);
       fg = fminf(fr, 0.f) - log1pf(expf(-fabsf(fr)));
     }
-    float a = fg, b = ig;                           // the map m -> max(m + a, b) of tokens t0 .. t
+    float a = fg, b = ig;                           // the map m -> max(m + a, b) of this warp's tokens up to t
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const float ap = __shfl_up_sync(0xffffffffu, a, off), bp = __shfl_up_sync(0xffffffffu, b, off);
@@ -1195,18 +1216,29 @@ mlstm_gate_scan_kernel(const T* __restrict__ raw_i, const T* __restrict__ raw_f,
         a = ap + a;
       }
     }
-    const float mcur = fmaxf(m + a, b);
+    if (lane == 31) wa[warp] = a, wb[warp] = b;
+    __syncthreads();
+    float pa = 0.f, pb = -INFINITY;                 // the map of the warps before this one
+    for (int w = 0; w < warp; ++w) {
+      pb = fmaxf(pb + wa[w], wb[w]);
+      pa += wa[w];
+    }
+    const float mstart = fmaxf(m + pa, pb);         // the maximum after the last token of the warps before
+    const float mcur = fmaxf(mstart + a, b);
     float mprev = __shfl_up_sync(0xffffffffu, mcur, 1);
-    if (lane == 0) mprev = m;
+    if (lane == 0) mprev = mstart;
     if (valid) {
       const long long o = (long long)(first + t) * H + h;
       decay[o] = expf(fg + mprev - mcur);
       beta[o] = expf(ig - mcur);
       mt[o] = mcur;
     }
-    m = __shfl_sync(0xffffffffu, mcur, 31);         // lanes past the end hold the identity map: m of the last token
+    if (threadIdx.x == blockDim.x - 1) carry = mcur;
+    __syncthreads();
+    m = carry;
   }
-  if (lane == 0) mstate[(long long)slot * H + h] = m;
+  (void)nw;
+  if (threadIdx.x == 0) mstate[(long long)slot * H + h] = m;
 }
 
 // One warp per (token, head): o fp32 [rows, H (dv + 1)] -> out = unit_rms(o[:dv] / (max(|o[dv]|, exp(-m)) + 1e-6)) * w *
@@ -1535,6 +1567,15 @@ SXB_API int sxb_bias_act_rows(const void* in, const void* bias, void* out, long 
                               void* stream) {
   const long long total = rows * F;
   if (total <= 0) return SXB_OK;
+  const int per = dtype == 0 ? 4 : 8;
+  if (F % per == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                        reinterpret_cast<uintptr_t>(bias)) & 15) == 0) {
+    const long long nv = total / per;
+    SEQMIX_DISPATCH(dtype, (bias_act_rows_vec_kernel<T><<<(unsigned)((nv + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                               (const T*)in, (const T*)bias, (T*)out, nv, F, act)));
+    SXB_CHECK_LAUNCH();
+    return SXB_OK;
+  }
   SEQMIX_DISPATCH(dtype, (bias_act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                              (const T*)in, (const T*)bias, (T*)out, total, F, act)));
   SXB_CHECK_LAUNCH();
@@ -1575,12 +1616,15 @@ SXB_API int sxb_mlstm_prepare(const void* proj, long long ld, void* buf, int n_t
 /* Gates of the matrix-memory LSTM: raw_i / raw_f (`dtype`, pitch ld, H channels), biases fp32 [H]; i = cap tanh((raw_i +
  * b_i) / cap), f = logsigmoid(cap tanh((raw_f + b_f) / cap)); m_t = max(f_t + m_(t-1), i_t) from mstate fp32 [slots, H]
  * (0 for a sequence that has seen no token; written back).  decay = exp(f + m_(t-1) - m_t), beta = exp(i - m_t), mt = m_t,
- * all fp32 [rows, H]. */
+ * all fp32 [n_tokens, H]. */
 SXB_API int sxb_mlstm_gate_scan(const void* raw_i, const void* raw_f, long long ld, const void* bias_i,
                                 const void* bias_f, float cap, void* mstate, void* decay, void* beta, void* mt,
-                                const void* seq_info, int n_seqs, int H, int dtype, void* stream) {
+                                const void* seq_info, int n_seqs, int n_tokens, int H, int dtype, void* stream) {
   if (n_seqs <= 0) return SXB_OK;
-  SEQMIX_DISPATCH(dtype, (mlstm_gate_scan_kernel<T><<<dim3(n_seqs, H), 32, 0, (cudaStream_t)stream>>>(
+  // threads per (sequence, head): the mean number of rows of a sequence, in whole warps
+  const int mean_rows = (n_tokens + n_seqs - 1) / n_seqs;
+  const int threads = std::min(kScanThreads, std::max(32, (mean_rows + 31) / 32 * 32));
+  SEQMIX_DISPATCH(dtype, (mlstm_gate_scan_kernel<T><<<dim3(n_seqs, H), threads, 0, (cudaStream_t)stream>>>(
                              (const T*)raw_i, (const T*)raw_f, ld, (const float*)bias_i, (const float*)bias_f, cap,
                              (float*)mstate, (float*)decay, (float*)beta, (float*)mt, (const int*)seq_info, H)));
   SXB_CHECK_LAUNCH();

@@ -510,7 +510,7 @@ int sxb_mlstm_prepare(const void* proj, long long ld, void* buf, int n_tokens, i
                       int dtype, void* stream);
 int sxb_mlstm_gate_scan(const void* raw_i, const void* raw_f, long long ld, const void* bias_i, const void* bias_f,
                         float cap, void* mstate, void* decay, void* beta, void* mt, const void* seq_info,
-                        int n_seqs, int H, int dtype, void* stream);
+                        int n_seqs, int n_tokens, int H, int dtype, void* stream);
 int sxb_mlstm_output(const void* o, const void* mt, const void* gate, long long ldg, const void* w, void* out,
                      int n_tokens, int H, int dv, float eps, int dtype, void* stream);
 

@@ -36,7 +36,7 @@ _lib.register({
     "sxb_bias_act_rows": "ppp" "l" "ii" "i" "p",
     "sxb_latent_qk_prepare": "p" "l" "p" "ll" "p" "l" "ppppppp" "iii" "iiiii" "f" "i" "p",
     "sxb_mlstm_prepare": "p" "l" "p" "iiii" "f" "i" "p",
-    "sxb_mlstm_gate_scan": "pp" "l" "pp" "f" "ppppp" "ii" "i" "p",
+    "sxb_mlstm_gate_scan": "pp" "l" "pp" "f" "ppppp" "iii" "i" "p",
     "sxb_mlstm_output": "ppp" "l" "pp" "iii" "f" "i" "p",
 })
 
@@ -513,7 +513,7 @@ def mlstm_gate_scan(raw_i: torch.Tensor, raw_f: torch.Tensor, bias_i: torch.Tens
         beta, mt = torch.empty_like(decay), torch.empty_like(decay)
         _lib.call("sxb_mlstm_gate_scan", _rows(raw_i).data_ptr(), _rows(raw_f).data_ptr(), raw_i.stride(0),
                   bias_i.data_ptr(), bias_f.data_ptr(), float(cap), mstate.data_ptr(), decay.data_ptr(), beta.data_ptr(),
-                  mt.data_ptr(), seq_info.data_ptr(), seq_info.shape[0], H, _dt(raw_i), _lib.stream_ptr())
+                  mt.data_ptr(), seq_info.data_ptr(), seq_info.shape[0], T, H, _dt(raw_i), _lib.stream_ptr())
         return decay, beta, mt
     ig = cap * torch.tanh((raw_i.float() + bias_i.float()) / cap)
     fg = torch.nn.functional.logsigmoid(cap * torch.tanh((raw_f.float() + bias_f.float()) / cap))
