@@ -83,7 +83,7 @@ def _scatter_fwd(x, assign, offsets, counts):
 def _gather_fwd(moe_out, scores, slots):
     T, K = slots.shape
     H = moe_out.shape[1]
-    if moe_out.is_cuda and moe_out.dtype == torch.bfloat16:
+    if moe_out.is_cuda and moe_out.dtype == torch.bfloat16 and H % 8 == 0:      # rows of whole 16-byte words
         out = torch.empty(T, H, dtype=moe_out.dtype, device=moe_out.device)
         _lib.call("sxb_moe_gather", moe_out.data_ptr(), out.data_ptr(), None if scores is None else scores.data_ptr(),
                   slots.data_ptr(), T, K, H, _lib.stream_ptr())
