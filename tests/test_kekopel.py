@@ -420,11 +420,12 @@ ODD = [
     make_cfg([dict(LATENT, mixer={"dim": 4, "heads": 2, "kv_rank": 24, "mask": {"size": 5}, "q_rank": 4,
                                   "rot": {"base": 10.0, "dims": 4}, "rot_dim": 8, "scale": 0.5, "vdim": 6},
                    mlp={"ff": 8, "kind": "dense"})] * 3, width=8, vocab=11, taps=2),
+    make_cfg([dict(MLSTM, mlp=None), MLSTM], width=16, vocab=23),
 ]
 
 
 @pytest.mark.parametrize("cfg", ODD, ids=["no_multiples_of_8_window_of_one_all_experts", "one_head_long_filter_window_past_prompt",
-                                          "same_layer_three_times_part_of_the_channels_turn"])
+                                          "same_layer_three_times_part_of_the_channels_turn", "no_attention_layer_no_cache"])
 def test_other_sizes(cfg):
     W = O.random_weights(cfg, seed=8)
     toks = tokens(21, cfg["vocab"], 9)
@@ -472,3 +473,44 @@ def test_greedy_generation_through_the_scheduler():
             seq.append(tok)
         assert len(out) == 6
     assert eng.free_blocks == 40 and eng._state_manager.n_tracked_sequences == 0
+
+
+def test_command_line_generation_from_a_checkpoint_folder(tmp_path):
+    """``config.json`` + ``model.safetensors`` (bf16) on disk, ``bin/sxb_generate`` picks the model class by the
+    configuration, loads the tensors by their checkpoint names and continues two prompts greedily."""
+    import json
+    import os
+    import struct
+    import subprocess
+    import sys
+    W = O.random_weights(MIXED, seed=14)
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(MIXED, f)
+    meta, blobs, off = {}, [], 0
+    for name, t in W.items():
+        b = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        meta[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    header = json.dumps(meta).encode()
+    with open(tmp_path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(header)) + header + b"".join(blobs))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompts = [[5, 17, 3], [9, 9, 1, 2, 3, 4, 5, 6, 7]]
+    cmd = [sys.executable, os.path.join(root, "bin", "sxb_generate"), "--model", str(tmp_path), "--max-new-tokens", "4",
+           "--dtype", "float32"]
+    for p in prompts:
+        cmd += ["--prompt", ",".join(map(str, p))]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert [x["prompt"] for x in lines] == prompts
+    for p, x in zip(prompts, lines):
+        seq = list(p)
+        for tok in x["generated"]:
+            logits = O.forward(seq, W, MIXED)[0][-1]
+            top2 = logits.topk(2).values
+            if top2[0] - top2[1] > 1e-3:
+                assert tok == int(logits.argmax())
+            seq.append(tok)
+        assert len(x["generated"]) == 4
